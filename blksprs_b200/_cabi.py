@@ -1,0 +1,97 @@
+"""ctypes binding of ``libblksprs_b200.so`` (the C ABI declared in ``include/blksprs_b200.h``).
+
+The library is the only compute path of this package: there is no Python or
+CPU fallback.  If it has not been built, every call raises ``RuntimeError``.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_int32, c_int64, c_size_t, c_void_p, c_char_p
+from pathlib import Path
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libblksprs_b200.so"
+
+# status codes (include/blksprs_b200.h)
+OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_RANGE, ERR_DEVICE_TIMEOUT = range(7)
+# matmul ops / kernel selectors / layout modes
+OP_NN, OP_NT, OP_TN = 0, 1, 2
+KERNEL_AUTO, KERNEL_MMA, KERNEL_UMMA = 0, 1, 2
+LAYOUT_EXACT, LAYOUT_FAST, LAYOUT_OUTER = 0, 1, 2
+
+LAYOUT_DTYPE_CODES = {
+    torch.bool: 0, torch.uint8: 0, torch.int8: 1, torch.int16: 2, torch.int32: 3, torch.int64: 4,
+    torch.float16: 5, torch.bfloat16: 6, torch.float32: 7, torch.float64: 8,
+}
+DATA_DTYPE_CODES = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+
+# name -> (restype, argtypes); must list every symbol the header declares
+SIGNATURES = {
+    "bsp_version": (c_int, []),
+    "bsp_status_string": (c_char_p, [c_int]),
+    "bsp_last_cuda_error": (c_char_p, []),
+    "bsp_lut_workspace_bytes": (c_size_t, [c_int64]),
+    "bsp_build_packed_indices": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "bsp_count_nonzero": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "bsp_build_layout_indices": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64,
+                                         c_void_p, c_size_t, c_void_p]),
+    "bsp_layout_matmul": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int,
+                                  c_void_p, c_void_p]),
+    "bsp_plan_count": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64,
+                               c_int64, c_int64, c_void_p, c_void_p]),
+    "bsp_plan_workspace_bytes": (c_size_t, [c_int64]),
+    "bsp_plan_offsets": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "bsp_plan_fill": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64,
+                              c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "bsp_plan_schedule": (c_int, [c_void_p, c_int64, c_int32, c_int32, c_void_p, c_void_p]),
+    "bsp_matmul_num_chunks": (c_int, [c_int, c_int, c_int]),
+    "bsp_matmul": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                           c_int32, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "bsp_transpose_blocks": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),
+}
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Returns the loaded library, loading it on first use."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"blksprs_b200: native library {LIB_PATH} is missing; there is no fallback path. "
+                "Build it with `python -m blksprs_b200.build`.")
+        handle = ctypes.CDLL(str(LIB_PATH))
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib
+
+
+class NativeError(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, status: int, where: str):
+        self.status = status
+        text = lib().bsp_status_string(status).decode()
+        detail = lib().bsp_last_cuda_error().decode() if status == ERR_CUDA else ""
+        super().__init__(f"blksprs_b200: {where} failed: {text}" + (f" [{detail}]" if detail else ""))
+
+
+def check(status: int, where: str) -> None:
+    if status != OK:
+        raise NativeError(status, where)
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    """Device pointer of a tensor (``None`` -> NULL)."""
+    if t is None:
+        return None
+    return t.data_ptr()
+
+
+def stream_handle(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream

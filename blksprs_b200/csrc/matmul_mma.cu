@@ -1,0 +1,300 @@
+// Block-sparse matmul on a pair plan with warp-level mma.sync tensor-core
+// instructions.  Serves the block sizes 16 and 32 (too small for a tcgen05
+// tile) and fp32 data (TF32 mma, like the reference's tl.dot on fp32 inputs,
+// blksprs/ops/matmul.py:242), and any other (dtype, bs) when asked for by
+// BSP_KERNEL_MMA.
+//
+// One CTA computes one TILE x TILE tile of one output block.  Per (pair,
+// k-chunk) step the two operand tiles are copied global -> shared with
+// cp.async, double buffered, always in their global orientation; whether an
+// operand is read transposed (BSP_OP_NT / BSP_OP_TN) is decided when the
+// fragments are read from shared memory (ldmatrix[.trans] for 16-bit data,
+// scalar loads for fp32).
+#include "common.cuh"
+
+namespace bsp {
+
+template <typename T> struct Elem;
+template <> struct Elem<__half> {
+    static constexpr bool k16 = true;
+    __device__ static inline void mma(float* c, const uint32_t* a, const uint32_t* b) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+    }
+    __device__ static inline void store2(__half* p, float x, float y) {
+        *reinterpret_cast<__half2*>(p) = __floats2half2_rn(x, y);
+    }
+};
+template <> struct Elem<__nv_bfloat16> {
+    static constexpr bool k16 = true;
+    __device__ static inline void mma(float* c, const uint32_t* a, const uint32_t* b) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+    }
+    __device__ static inline void store2(__nv_bfloat16* p, float x, float y) {
+        *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(x, y);
+    }
+};
+template <> struct Elem<float> {
+    static constexpr bool k16 = false;
+    __device__ static inline void mma(float* c, const uint32_t* a, const uint32_t* b) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+    }
+    __device__ static inline void store2(float* p, float x, float y) {
+        *reinterpret_cast<float2*>(p) = make_float2(x, y);
+    }
+};
+
+__device__ inline uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ inline void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst)), "l"(src));
+}
+__device__ inline void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ inline void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ inline uint32_t f32_to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ inline void ldmatrix_x4(uint32_t* r, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ inline void ldmatrix_x4_trans(uint32_t* r, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+
+// Row padding (in elements) of a shared-memory operand tile.  16-bit tiles are
+// read with ldmatrix (8 rows of 16 B must fall into distinct bank groups: +16 B).
+// fp32 tiles are read with scalar loads; a tile read along its rows by the
+// fragment's 8-wide index wants a stride of 4 (mod 32) words, one read along
+// its columns wants 8 (mod 32).
+template <typename T, bool FRAG_ROWS_ARE_8WIDE>
+struct Pad {
+    static constexpr int value = sizeof(T) == 2 ? 8 : (FRAG_ROWS_ARE_8WIDE ? 4 : 8);
+};
+
+template <typename T, int TILE, int OP>
+__global__ void __launch_bounds__(TILE == 16 ? 32 : 128)
+matmul_mma_kernel(const T* __restrict__ a, int64_t n_a, const T* __restrict__ b, int64_t n_b,
+                  T* __restrict__ out, const int32_t* __restrict__ offsets,
+                  const int32_t* __restrict__ pairs, int bs, int32_t* __restrict__ status_word) {
+    constexpr bool A_TRANS = (OP == BSP_OP_TN);  // shared A tile holds [k][m]
+    constexpr bool B_NK = (OP == BSP_OP_NT);     // shared B tile holds [n][k]
+    constexpr int NW = TILE == 16 ? 1 : 4;
+    constexpr int NT = NW * 32;
+    constexpr int WM = TILE == 16 ? 16 : TILE / 2;
+    constexpr int WN = TILE == 16 ? 16 : TILE / 2;
+    constexpr int MI = WM / 16, NI = WN / 8;
+    constexpr int APAD = Pad<T, !A_TRANS>::value;
+    constexpr int BPAD = Pad<T, B_NK>::value;
+    constexpr int ALD = TILE + APAD, BLD = TILE + BPAD;
+    constexpr int KSTEP = Elem<T>::k16 ? 16 : 8;
+    constexpr int CHUNK = 16 / sizeof(T);  // elements per 16-byte copy
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T* As = reinterpret_cast<T*>(smem_raw);  // [2][TILE][ALD]
+    T* Bs = As + 2 * TILE * ALD;             // [2][TILE][BLD]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int warp_m = NW == 1 ? 0 : warp >> 1, warp_n = NW == 1 ? 0 : warp & 1;
+    const int g = lane >> 2, t4 = lane & 3;
+
+    const int64_t p = blockIdx.x;
+    const int tiles = bs / TILE;
+    const int tm = blockIdx.y / tiles, tn = blockIdx.y % tiles;
+    const int beg = offsets[p], end = offsets[p + 1];
+    const int nkc = bs / TILE;
+    const int nsteps = (end - beg) * nkc;
+    const int64_t blk_elems = (int64_t)bs * bs;
+
+    float acc[MI][NI][4];
+#pragma unroll
+    for (int i = 0; i < MI; ++i)
+#pragma unroll
+        for (int j = 0; j < NI; ++j)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) acc[i][j][r] = 0.f;
+
+    // Copies the operand tiles of step s into buffer `buf`; returns false (and
+    // copies nothing) when the pair's indices are out of range.
+    auto issue = [&](int s, int buf) -> bool {
+        const int pr = beg + s / nkc, kc = s % nkc;
+        const int ia = pairs[2 * (int64_t)pr], ib = pairs[2 * (int64_t)pr + 1];
+        const bool ok = ia >= 0 && ia < n_a && ib >= 0 && ib < n_b;
+        if (ok) {
+            const int ar0 = A_TRANS ? kc * TILE : tm * TILE, ac0 = A_TRANS ? tm * TILE : kc * TILE;
+            const int br0 = B_NK ? tn * TILE : kc * TILE, bc0 = B_NK ? kc * TILE : tn * TILE;
+            const T* ga = a + ia * blk_elems + (int64_t)ar0 * bs + ac0;
+            const T* gb = b + ib * blk_elems + (int64_t)br0 * bs + bc0;
+            T* sa = As + buf * TILE * ALD;
+            T* sb = Bs + buf * TILE * BLD;
+            constexpr int CPR = TILE / CHUNK;  // 16-byte copies per tile row
+            for (int i = tid; i < TILE * CPR; i += NT) {
+                const int r = i / CPR, c = (i % CPR) * CHUNK;
+                cp_async16(sa + r * ALD + c, ga + (int64_t)r * bs + c);
+                cp_async16(sb + r * BLD + c, gb + (int64_t)r * bs + c);
+            }
+        } else if (status_word && tid == 0) {
+            *status_word = BSP_ERR_DEVICE_RANGE;
+        }
+        cp_async_commit();
+        return ok;
+    };
+
+    bool ok_cur = false, ok_next = false;
+    if (nsteps > 0) ok_cur = issue(0, 0);
+    for (int s = 0; s < nsteps; ++s) {
+        const int buf = s & 1;
+        if (s + 1 < nsteps) {
+            ok_next = issue(s + 1, buf ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (ok_cur) {
+            const T* sa = As + buf * TILE * ALD;
+            const T* sb = Bs + buf * TILE * BLD;
+#pragma unroll
+            for (int k0 = 0; k0 < TILE; k0 += KSTEP) {
+                uint32_t af[MI][4];
+                uint32_t bf[NI][2];
+                if constexpr (Elem<T>::k16) {
+                    const int q = lane >> 3, rr = lane & 7;
+#pragma unroll
+                    for (int i = 0; i < MI; ++i) {
+                        const int m0 = warp_m * WM + i * 16;
+                        if constexpr (!A_TRANS) {
+                            ldmatrix_x4(af[i], sa + (m0 + rr + (q & 1) * 8) * ALD + k0 + (q >> 1) * 8);
+                        } else {
+                            ldmatrix_x4_trans(af[i], sa + (k0 + rr + (q >> 1) * 8) * ALD + m0 + (q & 1) * 8);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < NI; j += 2) {
+                        const int n0 = warp_n * WN + j * 8;
+                        uint32_t r4[4];
+                        if constexpr (B_NK) {
+                            ldmatrix_x4(r4, sb + (n0 + rr + (q >> 1) * 8) * BLD + k0 + (q & 1) * 8);
+                        } else {
+                            ldmatrix_x4_trans(r4, sb + (k0 + rr + (q & 1) * 8) * BLD + n0 + (q >> 1) * 8);
+                        }
+                        bf[j][0] = r4[0]; bf[j][1] = r4[1];
+                        bf[j + 1][0] = r4[2]; bf[j + 1][1] = r4[3];
+                    }
+                } else {
+                    auto A_at = [&](int m, int k) -> float {
+                        return A_TRANS ? (float)sa[k * ALD + m] : (float)sa[m * ALD + k];
+                    };
+                    auto B_at = [&](int k, int n) -> float {
+                        return B_NK ? (float)sb[n * BLD + k] : (float)sb[k * BLD + n];
+                    };
+#pragma unroll
+                    for (int i = 0; i < MI; ++i) {
+                        const int m0 = warp_m * WM + i * 16;
+                        af[i][0] = f32_to_tf32(A_at(m0 + g, k0 + t4));
+                        af[i][1] = f32_to_tf32(A_at(m0 + g + 8, k0 + t4));
+                        af[i][2] = f32_to_tf32(A_at(m0 + g, k0 + t4 + 4));
+                        af[i][3] = f32_to_tf32(A_at(m0 + g + 8, k0 + t4 + 4));
+                    }
+#pragma unroll
+                    for (int j = 0; j < NI; ++j) {
+                        const int n0 = warp_n * WN + j * 8;
+                        bf[j][0] = f32_to_tf32(B_at(k0 + t4, n0 + g));
+                        bf[j][1] = f32_to_tf32(B_at(k0 + t4 + 4, n0 + g));
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < MI; ++i)
+#pragma unroll
+                    for (int j = 0; j < NI; ++j) Elem<T>::mma(acc[i][j], af[i], bf[j]);
+            }
+        }
+        __syncthreads();
+        ok_cur = ok_next;
+    }
+
+    T* o = out + p * blk_elems;
+#pragma unroll
+    for (int i = 0; i < MI; ++i)
+#pragma unroll
+        for (int j = 0; j < NI; ++j) {
+            const int row = tm * TILE + warp_m * WM + i * 16 + g;
+            const int col = tn * TILE + warp_n * WN + j * 8 + 2 * t4;
+            Elem<T>::store2(o + (int64_t)row * bs + col, acc[i][j][0], acc[i][j][1]);
+            Elem<T>::store2(o + (int64_t)(row + 8) * bs + col, acc[i][j][2], acc[i][j][3]);
+        }
+}
+
+template <typename T, int TILE, int OP>
+static int launch_one(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
+                      int64_t n_out, const int32_t* offsets, const int32_t* pairs, int bs,
+                      int32_t* status_word, cudaStream_t stream) {
+    constexpr bool A_TRANS = (OP == BSP_OP_TN), B_NK = (OP == BSP_OP_NT);
+    constexpr int ALD = TILE + Pad<T, !A_TRANS>::value, BLD = TILE + Pad<T, B_NK>::value;
+    constexpr size_t smem = (size_t)2 * TILE * (ALD + BLD) * sizeof(T);
+    auto kern = matmul_mma_kernel<T, TILE, OP>;
+    if (smem > 48 * 1024)
+        BSP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int tiles = bs / TILE;
+    dim3 grid((unsigned)n_out, (unsigned)(tiles * tiles));
+    kern<<<grid, TILE == 16 ? 32 : 128, smem, stream>>>((const T*)a, n_a, (const T*)b, n_b, (T*)out,
+                                                         offsets, pairs, bs, status_word);
+    BSP_LAUNCH_CHECK();
+    return BSP_OK;
+}
+
+template <typename T, int TILE>
+static int launch_op(int op, const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
+                     int64_t n_out, const int32_t* offsets, const int32_t* pairs, int bs,
+                     int32_t* status_word, cudaStream_t stream) {
+    switch (op) {
+        case BSP_OP_NN: return launch_one<T, TILE, BSP_OP_NN>(a, n_a, b, n_b, out, n_out, offsets, pairs, bs, status_word, stream);
+        case BSP_OP_NT: return launch_one<T, TILE, BSP_OP_NT>(a, n_a, b, n_b, out, n_out, offsets, pairs, bs, status_word, stream);
+        case BSP_OP_TN: return launch_one<T, TILE, BSP_OP_TN>(a, n_a, b, n_b, out, n_out, offsets, pairs, bs, status_word, stream);
+        default: return BSP_ERR_INVALID_ARG;
+    }
+}
+
+template <typename T>
+static int launch_tile(int op, const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
+                       int64_t n_out, const int32_t* offsets, const int32_t* pairs, int bs,
+                       int32_t* status_word, cudaStream_t stream) {
+    // fp32 tiles are capped at 32 to keep the double-buffered tiles small.
+    const int cap = sizeof(T) == 4 ? 32 : 64;
+    const int tile = bs < cap ? bs : cap;
+    if (tile == 16) return launch_op<T, 16>(op, a, n_a, b, n_b, out, n_out, offsets, pairs, bs, status_word, stream);
+    if (tile == 32) return launch_op<T, 32>(op, a, n_a, b, n_b, out, n_out, offsets, pairs, bs, status_word, stream);
+    if constexpr (sizeof(T) == 2) {
+        if (tile == 64) return launch_op<T, 64>(op, a, n_a, b, n_b, out, n_out, offsets, pairs, bs, status_word, stream);
+    }
+    return BSP_ERR_UNSUPPORTED;
+}
+
+int launch_matmul_mma(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
+                      int64_t n_out, const int32_t* offsets, const int32_t* pairs, int bs,
+                      int dtype, int op, int32_t* status_word, cudaStream_t stream) {
+    if (n_out > 0x7fffffffLL) return BSP_ERR_UNSUPPORTED;
+    const int tiles_cap = bs / (dtype == BSP_F32 ? 32 : 64);
+    if (tiles_cap > 0 && (int64_t)tiles_cap * tiles_cap > 65535) return BSP_ERR_UNSUPPORTED;
+    switch (dtype) {
+        case BSP_F16: return launch_tile<__half>(op, a, n_a, b, n_b, out, n_out, offsets, pairs, bs, status_word, stream);
+        case BSP_BF16: return launch_tile<__nv_bfloat16>(op, a, n_a, b, n_b, out, n_out, offsets, pairs, bs, status_word, stream);
+        case BSP_F32: return launch_tile<float>(op, a, n_a, b, n_b, out, n_out, offsets, pairs, bs, status_word, stream);
+        default: return BSP_ERR_UNSUPPORTED;
+    }
+}
+
+}  // namespace bsp

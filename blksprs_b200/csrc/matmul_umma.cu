@@ -1,0 +1,548 @@
+// Block-sparse matmul on a pair plan with 5th-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory) for 16-bit data and block sizes
+// 64 and 128.
+//
+// One persistent CTA per SM walks a contiguous range of output blocks
+// (bsp_plan_schedule).  Roles, by warp:
+//   warp 0      producer: streams the range's (a_block, b_block) pairs, and for
+//               each pair TMA-loads the two bs x bs operand blocks (128-byte
+//               swizzle, global orientation) into the next free ring stage
+//   warp 1      MMA issuer: one thread issues bs/16 tcgen05.mma per pair into
+//               the current accumulator, releases the stage with
+//               tcgen05.commit, and hands a finished accumulator to the
+//               epilogue
+//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator, convert to the
+//               output type, write the output block; blocks without pairs are
+//               written as zeros without touching tensor memory
+// The transposed products of the backward pass (BSP_OP_NT, BSP_OP_TN) use the
+// same staged blocks; only the major-ness bits of the shared-memory matrix
+// descriptors and of the instruction descriptor change.
+//
+// Every wait is bounded (about one second); a wait that runs out records
+// BSP_ERR_DEVICE_TIMEOUT in the status word, all roles leave their loops,
+// outstanding copies and MMAs are drained with bounded waits, tensor memory is
+// freed and the kernel returns.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace bsp {
+
+namespace {
+
+constexpr int kThreads = 192;
+constexpr uint32_t kFlagLast = 1u;  // stage holds the last pair of its output block
+constexpr unsigned long long kWaitLimitNs = 1000000000ull;
+
+template <int BS> struct Cfg;
+template <> struct Cfg<64> {
+    static constexpr int kStages = 8;     // 8 x 16 KiB
+    static constexpr int kAccs = 4;       // 4 x 64 columns
+    static constexpr int kTmemCols = 256;
+};
+template <> struct Cfg<128> {
+    static constexpr int kStages = 3;     // 3 x 64 KiB
+    static constexpr int kAccs = 4;       // 4 x 128 columns
+    static constexpr int kTmemCols = 512;
+};
+
+template <int BS>
+struct SmemLayout {
+    static constexpr int kBlockBytes = BS * BS * 2;
+    static constexpr int kStageBytes = 2 * kBlockBytes;
+    static constexpr int kDataBytes = Cfg<BS>::kStages * kStageBytes;
+    // after the data: full[S], empty[S], tmem_full[A], tmem_empty[A], drain (8 B each),
+    // flags[S] (4 B), armed[S] (4 B), tmem base (4 B), abort flag (4 B)
+    static constexpr int kBarBytes = (2 * Cfg<BS>::kStages + 2 * Cfg<BS>::kAccs + 1) * 8;
+    static constexpr int kMiscBytes = (2 * Cfg<BS>::kStages + 2) * 4;
+    static constexpr int kTotal = kDataBytes + kBarBytes + kMiscBytes + 1024 /* alignment slack */;
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ unsigned long long global_timer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+// Bounded wait: false if the limit ran out or another role already gave up.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            int32_t* status_word) {
+    const unsigned long long t0 = global_timer();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 0xff) == 0) {
+            if (*abort_flag) return false;
+            if (global_timer() - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                if (status_word) *status_word = BSP_ERR_DEVICE_TIMEOUT;
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* status_word) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status_word);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                           uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), sm_100
+// descriptor version 1.  Offsets are in bytes; the fields drop the 4 LSBs.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float x, float y);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float x, float y) {
+    __half2 h = __floats2half2_rn(x, y);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float x, float y) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// A staged operand block is bs rows of bs 16-bit elements, split into column
+// panels of 64 elements (128 B): panel h lives at h * bs * 128 bytes, row r of
+// a panel at r * 128, 16-byte chunks XOR-swizzled by (r % 8).
+//
+// Read K-major (the contraction index runs along the rows' 64-element panels):
+//   8-row groups are 1024 B apart (SBO); k-step s (16 elements) starts
+//   (s / 4) panels in, (s % 4) * 32 bytes into the 128-byte row.
+// Read MN-major (the contraction index runs down the rows):
+//   the 64-wide panels are the M/N atoms, bs * 128 bytes apart (LBO); 8-row
+//   k-groups are 1024 B apart (SBO); k-step s starts 16 rows = 2048 B further.
+template <int BS, bool MN_MAJOR>
+__device__ __forceinline__ uint64_t operand_desc(uint32_t base, int kstep) {
+    if (MN_MAJOR) return make_smem_desc(base + kstep * 2048, BS * 128, 1024);
+    return make_smem_desc(base + (kstep >> 2) * (BS * 128) + (kstep & 3) * 32, 16, 1024);
+}
+
+template <typename T, int BS, int OP>
+__global__ void __launch_bounds__(kThreads, 1)
+matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   int64_t n_a, int64_t n_b, T* __restrict__ out,
+                   const int32_t* __restrict__ offsets, const int32_t* __restrict__ pairs,
+                   const int32_t* __restrict__ chunk_begin, uint32_t idesc,
+                   int32_t* __restrict__ status_word) {
+    using C = Cfg<BS>;
+    using L = SmemLayout<BS>;
+    constexpr int S = C::kStages, A = C::kAccs;
+    constexpr bool A_MN = (OP == BSP_OP_TN);   // A block is read transposed
+    constexpr bool B_MN = (OP != BSP_OP_NT);   // B block rows are the contraction index
+    constexpr int KSTEPS = BS / 16;
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_addr(smem_raw);
+    const uint32_t data = (raw + 1023u) & ~1023u;
+    unsigned char* data_ptr = smem_raw + (data - raw);
+    const uint32_t bars = data + L::kDataBytes;
+    const uint32_t full_bar = bars, empty_bar = bars + 8 * S, tfull_bar = bars + 16 * S,
+                   tempty_bar = tfull_bar + 8 * A, drain_bar = tempty_bar + 8 * A;
+    volatile uint32_t* flags = reinterpret_cast<volatile uint32_t*>(data_ptr + L::kDataBytes + L::kBarBytes);
+    volatile int* armed = reinterpret_cast<volatile int*>(flags + S);
+    volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(armed + S);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int blk_begin = chunk_begin[blockIdx.x], blk_end = chunk_begin[blockIdx.x + 1];
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+            armed[s] = -1;
+        }
+        for (int i = 0; i < A; ++i) {
+            mbar_init(tfull_bar + 8 * i, 1);
+            mbar_init(tempty_bar + 8 * i, 4);
+        }
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_addr((const void*)tmem_base_slot)), "r"((uint32_t)C::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (blk_begin < blk_end) {
+        const int pr_begin = offsets[blk_begin], pr_end = offsets[blk_end];
+
+        if (warp == 0) {
+            // ---------------- producer ----------------
+            const int2* pairs2 = reinterpret_cast<const int2*>(pairs);
+            int stage = 0;
+            uint32_t phase = 0;
+            int blk = blk_begin;
+            // window of block end offsets: lane l holds offsets[win + l + 1]
+            int win = blk_begin;
+            auto load_window = [&](int w) -> int {
+                const int i = w + lane + 1;
+                return i <= blk_end ? offsets[i] : 0x7fffffff;
+            };
+            int win_cur = load_window(win);
+            int win_nxt = load_window(win + 32);
+            auto load_batch = [&](int p0) -> int2 {
+                const int i = p0 + lane;
+                return i < pr_end ? pairs2[i] : make_int2(0, 0);
+            };
+            int2 batch_cur = load_batch(pr_begin);
+            bool alive = true;
+            for (int p0 = pr_begin; p0 < pr_end && alive; p0 += 32) {
+                const int2 batch_nxt = load_batch(p0 + 32);
+                const int m = min(32, pr_end - p0);
+                for (int j = 0; j < m && alive; ++j) {
+                    const int pr = p0 + j;
+                    int ia = __shfl_sync(0xffffffffu, batch_cur.x, j);
+                    int ib = __shfl_sync(0xffffffffu, batch_cur.y, j);
+                    // advance the block cursor to the block that owns pair `pr`
+                    int cur_end;
+                    for (;;) {
+                        if (blk - win >= 32) {
+                            win += 32;
+                            win_cur = win_nxt;
+                            win_nxt = load_window(win + 32);
+                        }
+                        cur_end = __shfl_sync(0xffffffffu, win_cur, blk - win);
+                        if (cur_end > pr) break;
+                        ++blk;
+                    }
+                    if (lane == 0) {
+                        if (ia < 0 || ia >= n_a || ib < 0 || ib >= n_b) {
+                            if (status_word) *status_word = BSP_ERR_DEVICE_RANGE;
+                            ia = 0;
+                            ib = 0;
+                        }
+                        if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status_word)) {
+                            alive = false;
+                        } else {
+                            // the MMA thread starts a new accumulator after each "last" pair
+                            flags[stage] = (pr + 1 == cur_end) ? kFlagLast : 0u;
+                            const uint32_t sa = data + stage * L::kStageBytes;
+                            const uint32_t sb = sa + L::kBlockBytes;
+                            const uint32_t bar = full_bar + 8 * stage;
+                            armed[stage] = (int)phase;
+                            mbar_arrive_expect_tx(bar, L::kStageBytes);
+#pragma unroll
+                            for (int h = 0; h < BS / 64; ++h) {
+                                tma_load_2d(sa + h * (BS * 128), &map_a, h * 64, ia * BS, bar);
+                                tma_load_2d(sb + h * (BS * 128), &map_b, h * 64, ib * BS, bar);
+                            }
+                        }
+                    }
+                    alive = __shfl_sync(0xffffffffu, (int)alive, 0) != 0;
+                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                }
+                batch_cur = batch_nxt;
+            }
+        } else if (warp == 1) {
+            // ---------------- MMA issuer ----------------
+            if (lane == 0) {
+                int stage = 0, acc = 0;
+                uint32_t phase = 0, acc_phase = 0;
+                bool first = true, alive = true;
+                for (int pr = pr_begin; pr < pr_end && alive; ++pr) {
+                    if (first) {
+                        if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, status_word)) break;
+                    }
+                    if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status_word)) break;
+                    tc_fence_after();
+                    const uint32_t fl = flags[stage];
+                    const uint32_t sa = data + stage * L::kStageBytes;
+                    const uint32_t sb = sa + L::kBlockBytes;
+                    const uint32_t d_tmem = tmem_base + acc * BS;
+#pragma unroll
+                    for (int k = 0; k < KSTEPS; ++k) {
+                        tc_mma_f16(d_tmem, operand_desc<BS, A_MN>(sa, k), operand_desc<BS, B_MN>(sb, k),
+                                   idesc, (first && k == 0) ? 0u : 1u);
+                    }
+                    tc_commit(empty_bar + 8 * stage);
+                    first = false;
+                    if (fl & kFlagLast) {
+                        tc_commit(tfull_bar + 8 * acc);
+                        first = true;
+                        if (++acc == A) { acc = 0; acc_phase ^= 1u; }
+                    }
+                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                }
+                // make sure no MMA is still running before tensor memory is freed
+                tc_commit(drain_bar);
+                mbar_wait(drain_bar, 0, abort_flag, status_word);
+            }
+        } else {
+            // ---------------- epilogue ----------------
+            const int q = warp & 3;  // tensor-memory subpartition of this warp
+            constexpr int ROWS_PER_WARP = BS / 4;
+            const bool row_valid = lane < ROWS_PER_WARP;
+            const int row = q * ROWS_PER_WARP + lane;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool alive = true;
+            for (int w0 = blk_begin; w0 < blk_end && alive; w0 += 32) {
+                const int bi = w0 + lane;
+                const int my_n = bi < blk_end ? offsets[bi + 1] - offsets[bi] : 0;
+                const int m = min(32, blk_end - w0);
+                for (int j = 0; j < m && alive; ++j) {
+                    const int n = __shfl_sync(0xffffffffu, my_n, j);
+                    T* o = out + (int64_t)(w0 + j) * BS * BS;
+                    if (n == 0) {
+                        // this warp zeroes its quarter of the block
+                        uint4* dst = reinterpret_cast<uint4*>(o + (int64_t)q * ROWS_PER_WARP * BS);
+                        constexpr int VECS = ROWS_PER_WARP * BS * 2 / 16;
+                        for (int i = lane; i < VECS; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
+                        continue;
+                    }
+                    if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, status_word)) {
+                        alive = false;
+                    }
+                    alive = __all_sync(0xffffffffu, alive);
+                    if (!alive) break;
+                    tc_fence_after();
+                    const uint32_t taddr = tmem_base + acc * BS + ((uint32_t)(q * 32) << 16);
+#pragma unroll
+                    for (int c0 = 0; c0 < BS; c0 += 32) {
+                        uint32_t v[32];
+                        tc_ld32(taddr + c0, v);
+                        tc_wait_ld();
+                        if (row_valid) {
+                            uint4* dst = reinterpret_cast<uint4*>(o + (int64_t)row * BS + c0);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                uint4 u;
+                                u.x = pack2<T>(__uint_as_float(v[8 * i + 0]), __uint_as_float(v[8 * i + 1]));
+                                u.y = pack2<T>(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]));
+                                u.z = pack2<T>(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]));
+                                u.w = pack2<T>(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]));
+                                dst[i] = u;
+                            }
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
+                    if (++acc == A) { acc = 0; acc_phase ^= 1u; }
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        // bounded wait for copies that were issued but never consumed
+        for (int s = 0; s < S; ++s) {
+            const int ph = armed[s];
+            if (ph >= 0) {
+                const unsigned long long t0 = global_timer();
+                while (!mbar_try_wait(full_bar + 8 * s, (uint32_t)ph)) {
+                    if (global_timer() - t0 > kWaitLimitNs) break;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)C::kTmemCols) : "memory");
+    }
+}
+
+// ---- host side -------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// 2-D view (n_blocks * bs rows, bs columns) of a compressed tensor, boxes of
+// bs rows x 64 columns, 128-byte swizzle.
+int make_block_map(CUtensorMap* map, const void* base, int64_t n_blocks, int bs, int dtype) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) {
+        set_cuda_error(cudaErrorNotSupported, "cuTensorMapEncodeTiled entry point");
+        return BSP_ERR_CUDA;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)bs, (cuuint64_t)(n_blocks * bs)};
+    cuuint64_t strides[1] = {(cuuint64_t)bs * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)bs};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, dtype == BSP_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                    2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+        return BSP_ERR_CUDA;
+    }
+    return BSP_OK;
+}
+
+uint32_t make_idesc(int dtype, int bs, int op) {
+    const uint32_t fmt = dtype == BSP_F16 ? 0u : 1u;
+    const uint32_t a_mn = op == BSP_OP_TN ? 1u : 0u;
+    const uint32_t b_mn = op != BSP_OP_NT ? 1u : 0u;
+    return (1u << 4)                       // fp32 accumulator
+           | (fmt << 7) | (fmt << 10)      // A and B element format
+           | (a_mn << 15) | (b_mn << 16)   // major-ness
+           | ((uint32_t)(bs >> 3) << 17)   // N
+           | ((uint32_t)(bs >> 4) << 24);  // M
+}
+
+int num_sms() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+template <typename T, int BS, int OP>
+int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_t n_b, void* out,
+               const int32_t* offsets, const int32_t* pairs, const int32_t* chunk_begin,
+               int32_t n_chunks, int dtype, int32_t* status_word, cudaStream_t stream) {
+    auto kern = matmul_umma_kernel<T, BS, OP>;
+    constexpr int smem = SmemLayout<BS>::kTotal;
+    BSP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<n_chunks, kThreads, smem, stream>>>(ma, mb, n_a, n_b, (T*)out, offsets, pairs, chunk_begin,
+                                               make_idesc(dtype, BS, OP), status_word);
+    BSP_LAUNCH_CHECK();
+    return BSP_OK;
+}
+
+template <typename T, int BS>
+int launch_op(int op, const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_t n_b, void* out,
+              const int32_t* offsets, const int32_t* pairs, const int32_t* chunk_begin, int32_t n_chunks,
+              int dtype, int32_t* status_word, cudaStream_t stream) {
+    switch (op) {
+        case BSP_OP_NN: return launch_cfg<T, BS, BSP_OP_NN>(ma, mb, n_a, n_b, out, offsets, pairs, chunk_begin, n_chunks, dtype, status_word, stream);
+        case BSP_OP_NT: return launch_cfg<T, BS, BSP_OP_NT>(ma, mb, n_a, n_b, out, offsets, pairs, chunk_begin, n_chunks, dtype, status_word, stream);
+        case BSP_OP_TN: return launch_cfg<T, BS, BSP_OP_TN>(ma, mb, n_a, n_b, out, offsets, pairs, chunk_begin, n_chunks, dtype, status_word, stream);
+        default: return BSP_ERR_INVALID_ARG;
+    }
+}
+
+}  // namespace
+
+bool umma_applicable(int dtype, int bs) {
+    return (dtype == BSP_F16 || dtype == BSP_BF16) && (bs == 64 || bs == 128);
+}
+
+int umma_num_chunks(int dtype, int bs) {
+    if (!umma_applicable(dtype, bs)) return 0;
+    return num_sms();
+}
+
+int launch_matmul_umma(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
+                       int64_t n_out, const int32_t* offsets, const int32_t* pairs,
+                       const int32_t* chunk_begin, int32_t n_chunks, int bs, int dtype, int op,
+                       int32_t* status_word, cudaStream_t stream) {
+    if (!umma_applicable(dtype, bs)) return BSP_ERR_UNSUPPORTED;
+    if (!chunk_begin || n_chunks < 1 || n_a < 1 || n_b < 1) return BSP_ERR_INVALID_ARG;
+    // TMA coordinates are 32-bit row indices into the (n_blocks * bs)-row view.
+    if (n_a * bs > 0x7fffffffLL || n_b * bs > 0x7fffffffLL || n_out > 0x7fffffffLL)
+        return BSP_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) ||
+        (reinterpret_cast<uintptr_t>(out) & 15))
+        return BSP_ERR_INVALID_ARG;
+    CUtensorMap ma, mb;
+    int st = make_block_map(&ma, a, n_a, bs, dtype);
+    if (st != BSP_OK) return st;
+    st = make_block_map(&mb, b, n_b, bs, dtype);
+    if (st != BSP_OK) return st;
+    if (dtype == BSP_F16) {
+        if (bs == 64) return launch_op<__half, 64>(op, ma, mb, n_a, n_b, out, offsets, pairs, chunk_begin, n_chunks, dtype, status_word, stream);
+        return launch_op<__half, 128>(op, ma, mb, n_a, n_b, out, offsets, pairs, chunk_begin, n_chunks, dtype, status_word, stream);
+    }
+    if (bs == 64) return launch_op<__nv_bfloat16, 64>(op, ma, mb, n_a, n_b, out, offsets, pairs, chunk_begin, n_chunks, dtype, status_word, stream);
+    return launch_op<__nv_bfloat16, 128>(op, ma, mb, n_a, n_b, out, offsets, pairs, chunk_begin, n_chunks, dtype, status_word, stream);
+}
+
+}  // namespace bsp

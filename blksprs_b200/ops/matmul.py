@@ -1,0 +1,192 @@
+"""Block-sparse matrix product ``bs.ops.matmul`` on the B200-native kernels.
+
+Drop-in for the reference op (blksprs/ops/matmul.py:17-67): same signature,
+same validation errors, same layout-cache entries (``packed_indices_x``,
+``packed_indices_y``, ``layout_indices_o``, ``n_sparse_blocks`` — bit-identical
+tensors), same ``BlksprsTensor`` result.  The forward product and the two
+backward products (``dX = dO·Yᵀ`` on x's layout, ``dY = Xᵀ·dO`` on y's layout,
+blksprs/ops/matmul.py:130-145) each run as one launch of the native library on a
+pre-built pair plan; no transposed copy of an operand is ever materialised.
+"""
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from .. import _cabi
+from ..plan import PairPlan, build_pair_plan, run_pair_plan
+from ..utils.blksprs_tensor import BlksprsTensor
+from ..utils.tools import build_layout_indices, build_packed_indices, cast_for_autocast, count_active_blocks, \
+    finalize_layout_cache, prepare_layout_cache
+from ..utils.validation import ensure_contiguous, validate_contiguous, validate_device, validate_dimensions, \
+    validate_dtype_float, validate_shape, validate_sparsity, validate_sparsity_block_size, \
+    validate_sparsity_layout, validation_enabled
+
+_PLANS = "_b200_plans"
+
+
+class _MatmulPlans:
+    """Private cache entry: pair plans and the extra LUTs the backward products need.
+
+    Lives in the layout cache as one opaque value, so filling in the backward
+    plans later does not change the cache's recorded state.
+    """
+
+    def __init__(self, sl_x: Tensor, sl_y: Tensor, sl_o: Tensor):
+        self.layouts = (sl_x, sl_y, sl_o)
+        self.n_x: int | None = None
+        self.n_y: int | None = None
+        self.forward: PairPlan | None = None
+        self.grad_x: PairPlan | None = None
+        self.grad_y: PairPlan | None = None
+        self.packed_o: Tensor | None = None
+
+    def dims(self):
+        sl_x, sl_y, _ = self.layouts
+        return sl_x.size(1), sl_x.size(2), sl_y.size(2)  # R, K, C
+
+
+def _n_chunks() -> int:
+    return _cabi.lib().bsp_matmul_num_chunks(_cabi.DATA_DTYPE_CODES[torch.bfloat16], 64, _cabi.KERNEL_AUTO)
+
+
+def matmul_build_layout_cache(layout_cache: dict | None, sparsity_layout_x: Tensor, sparsity_layout_y: Tensor,
+                              sparsity_layout_output: Tensor) -> dict:
+    """Builds or reuses the matmul metadata (blksprs/ops/matmul.py:256-279 plus the pair plans)."""
+    layout_cache = prepare_layout_cache(layout_cache, "matmul", sparsity_layout_x, sparsity_layout_y,
+                                        sparsity_layout_output)
+
+    if "packed_indices_x" not in layout_cache:
+        layout_cache["packed_indices_x"] = build_packed_indices(sparsity_layout_x)
+    if "packed_indices_y" not in layout_cache:
+        layout_cache["packed_indices_y"] = build_packed_indices(sparsity_layout_y)
+    if "n_sparse_blocks" not in layout_cache:
+        layout_cache["n_sparse_blocks"] = count_active_blocks(sparsity_layout_output)
+    if "layout_indices_o" not in layout_cache:
+        layout_cache["layout_indices_o"] = build_layout_indices(sparsity_layout_output,
+                                                                layout_cache["n_sparse_blocks"])
+    if _PLANS not in layout_cache:
+        layout_cache[_PLANS] = _MatmulPlans(sparsity_layout_x, sparsity_layout_y, sparsity_layout_output)
+    plans: _MatmulPlans = layout_cache[_PLANS]
+    if plans.forward is None:
+        R, K, C = plans.dims()
+        plans.forward = build_pair_plan(_cabi.OP_NN, layout_cache["layout_indices_o"],
+                                        layout_cache["packed_indices_x"], layout_cache["packed_indices_y"],
+                                        R, K, C, _n_chunks())
+
+    validate_contiguous(sparsity_layout_x, layout_cache["packed_indices_x"],
+                        sparsity_layout_y, layout_cache["packed_indices_y"],
+                        sparsity_layout_output, layout_cache["layout_indices_o"])
+    return finalize_layout_cache(layout_cache)
+
+
+def _backward_plans(plans: _MatmulPlans, packed_x: Tensor, packed_y: Tensor, n_x: int, n_y: int) -> None:
+    """Fills in the plans of the two backward products (once per layout triple)."""
+    if plans.grad_x is not None and plans.grad_y is not None:
+        return
+    sl_x, sl_y, sl_o = plans.layouts
+    R, K, C = plans.dims()
+    if plans.packed_o is None:
+        plans.packed_o = build_packed_indices(sl_o)
+    chunks = _n_chunks()
+    if plans.grad_x is None:
+        lut_x = build_layout_indices(sl_x, n_x)
+        plans.grad_x = build_pair_plan(_cabi.OP_NT, lut_x, plans.packed_o, packed_y, R, K, C, chunks)
+    if plans.grad_y is None:
+        lut_y = build_layout_indices(sl_y, n_y)
+        plans.grad_y = build_pair_plan(_cabi.OP_TN, lut_y, packed_x, plans.packed_o, R, K, C, chunks)
+
+
+class _BlockSparseMatmul(torch.autograd.Function):
+    """Differentiable in ``x`` and ``y``; layouts, LUTs and plans are constants."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, y: Tensor, packed_x: Tensor, packed_y: Tensor, plans: _MatmulPlans, bs: int):
+        ctx.save_for_backward(x, y, packed_x, packed_y)
+        ctx.plans = plans
+        ctx.sparsity_block_size = bs
+        return run_pair_plan(plans.forward, x, y, bs)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad_output: Tensor):
+        x, y, packed_x, packed_y = ctx.saved_tensors
+        plans: _MatmulPlans = ctx.plans
+        bs = ctx.sparsity_block_size
+        grad_output = grad_output.contiguous()
+        if grad_output.dtype != x.dtype:
+            grad_output = grad_output.to(x.dtype)
+        need_x, need_y = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        _backward_plans(plans, packed_x, packed_y, x.size(0), y.size(0))
+        grad_x = run_pair_plan(plans.grad_x, grad_output, y, bs) if need_x else None
+        grad_y = run_pair_plan(plans.grad_y, x, grad_output, bs) if need_y else None
+        return grad_x, grad_y, None, None, None, None
+
+
+@torch.compiler.disable
+def _matmul_eager(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_output, sparsity_block_size,
+                  layout_cache):
+    x, y = ensure_contiguous(x, y)
+    x, y = cast_for_autocast(x, y)
+
+    validate_dimensions(x, y)
+    validate_contiguous(x, y, sparsity_layout_output)
+    validate_dtype_float(x, y)
+    validate_device(x, y, sparsity_layout_output)
+
+    # A warm cache already knows how many blocks each layout holds, which saves
+    # the two device reads of the block-count check.
+    counts = None
+    if layout_cache is not None and validation_enabled():
+        probe = prepare_layout_cache(layout_cache, "matmul", sparsity_layout_x, sparsity_layout_y,
+                                     sparsity_layout_output)
+        plans = probe.get(_PLANS)
+        if plans is not None and plans.n_x is not None:
+            counts = (plans.n_x, plans.n_y)
+    validate_sparsity(sparsity_block_size, (x, sparsity_layout_x), (y, sparsity_layout_y), counts=counts)
+    validate_sparsity_layout(sparsity_layout_output)
+    if sparsity_layout_x.size(0) != sparsity_layout_y.size(0):
+        raise ValueError("Batch dimensions of tensors must match")
+    if sparsity_layout_x.size(-1) != sparsity_layout_y.size(-2):
+        raise ValueError("Inner dimensions of tensors must match")
+    validate_shape(sparsity_layout_output,
+                   (sparsity_layout_x.size(0), sparsity_layout_x.size(1), sparsity_layout_y.size(2)),
+                   "Output sparsity layout")
+    validate_sparsity_block_size(sparsity_block_size, x, y)
+
+    layout_cache = matmul_build_layout_cache(layout_cache, sparsity_layout_x, sparsity_layout_y,
+                                             sparsity_layout_output)
+    plans = layout_cache[_PLANS]
+    if plans.n_x is None and validation_enabled():
+        # validate_sparsity has just confirmed these against the layouts
+        plans.n_x, plans.n_y = x.size(0), y.size(0)
+
+    out = _BlockSparseMatmul.apply(x, y, layout_cache["packed_indices_x"], layout_cache["packed_indices_y"],
+                                   plans, sparsity_block_size)
+    return BlksprsTensor.wrap(out)
+
+
+@torch.amp.custom_fwd(device_type="cuda")
+def matmul(x: BlksprsTensor, sparsity_layout_x: Tensor,
+           y: BlksprsTensor, sparsity_layout_y: Tensor,
+           sparsity_layout_output: Tensor,
+           sparsity_block_size: int, layout_cache: dict | None = None) -> BlksprsTensor:
+    """Multiplies two compressed block-sparse tensors.
+
+    Only blocks marked active by ``sparsity_layout_output`` are calculated; active output
+    blocks without a common inner block are zero.
+
+    Args:
+        x (BlksprsTensor): The compressed left operand.
+        sparsity_layout_x (Tensor): The sparsity layout of ``x``.
+        y (BlksprsTensor): The compressed right operand.
+        sparsity_layout_y (Tensor): The sparsity layout of ``y``.
+        sparsity_layout_output (Tensor): The sparsity layout of the output tensor.
+        sparsity_block_size (int): The size of the sparsity blocks.
+        layout_cache (dict, optional): Reusable layout metadata cache (default ``None``).
+
+    Returns:
+        BlksprsTensor: The matrix product in compressed form.
+    """
+    return _matmul_eager(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_output,
+                         sparsity_block_size, layout_cache)

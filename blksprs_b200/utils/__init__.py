@@ -1,0 +1,16 @@
+"""Host-side helpers of the matmul path: compressed-tensor marker, validation switches, shape helpers."""
+from . import validation
+from .blksprs_tensor import BlksprsTensor
+from .tools import do_shape_blocksparse, undo_shape_blocksparse
+from .validation import disable_contiguous, disable_validation, enable_contiguous, enable_validation
+
+__all__ = [
+    "BlksprsTensor",
+    "disable_contiguous",
+    "disable_validation",
+    "do_shape_blocksparse",
+    "enable_contiguous",
+    "enable_validation",
+    "undo_shape_blocksparse",
+    "validation",
+]

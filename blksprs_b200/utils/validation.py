@@ -1,0 +1,167 @@
+"""Input validation of the matmul path, with the reference's exception types and messages.
+
+Covers the validators ``bs.ops.matmul`` and the matmul layout helpers call
+(blksprs/utils/validation.py:54-99, 179-205, 297-386) and the thread-local
+switches ``disable/enable_validation`` and ``disable/enable_contiguous``
+(blksprs/utils/validation.py:447-472).
+"""
+from __future__ import annotations
+
+import threading
+
+import torch
+from torch import Tensor
+
+_state = threading.local()
+
+_FLOAT_DTYPES = (torch.float16, torch.bfloat16, torch.float32)
+_SUPPORTED_MOVE_DTYPES = (torch.bool, torch.uint8, torch.int8, torch.int16, torch.int32, torch.int64,
+                          torch.float16, torch.bfloat16, torch.float32, torch.float64)
+
+
+def validation_enabled() -> bool:
+    return getattr(_state, "validation", True)
+
+
+def contiguous_enabled() -> bool:
+    return getattr(_state, "contiguous", True)
+
+
+def disable_validation() -> None:
+    """Turns input validation off for the calling thread."""
+    _state.validation = False
+
+
+def enable_validation() -> None:
+    """Turns input validation on for the calling thread."""
+    _state.validation = True
+
+
+def disable_contiguous() -> None:
+    """Stops ops from calling ``.contiguous()`` on their inputs (calling thread only)."""
+    _state.contiguous = False
+
+
+def enable_contiguous() -> None:
+    """Lets ops call ``.contiguous()`` on their inputs (calling thread only)."""
+    _state.contiguous = True
+
+
+def ensure_contiguous(*tensors: Tensor):
+    """Contiguous versions of ``tensors`` unless the thread-local switch is off."""
+    if contiguous_enabled():
+        tensors = tuple(t.contiguous() for t in tensors)
+    return tensors[0] if len(tensors) == 1 else tensors
+
+
+def validate_dimensions(*tensors: Tensor, dims: int = 3) -> None:
+    if not validation_enabled():
+        return
+    if any(t.dim() != dims for t in tensors):
+        raise ValueError(f"Tensor must have {dims} dimensions")
+
+
+def validate_contiguous(*tensors: Tensor) -> None:
+    if not validation_enabled():
+        return
+    if not all(t.is_contiguous() for t in tensors):
+        raise ValueError("Tensor must be contiguous")
+
+
+def validate_dtype_float(*tensors: Tensor) -> None:
+    """All tensors fp16 / bf16 / fp32 and of one dtype."""
+    if not validation_enabled():
+        return
+    for t in tensors:
+        if t.dtype not in _FLOAT_DTYPES:
+            raise ValueError("Tensor must have either float16, bfloat16, or float32 dtype")
+        if t.dtype != tensors[0].dtype:
+            raise ValueError("Tensors must have same dtype")
+
+
+def validate_dtype_supported(*tensors: Tensor) -> None:
+    if not validation_enabled():
+        return
+    if any(t.dtype not in _SUPPORTED_MOVE_DTYPES for t in tensors):
+        raise ValueError("Tensor dtype is not supported")
+
+
+def validate_device(*tensors: Tensor) -> None:
+    """All tensors on one CUDA device."""
+    if not validation_enabled() or not tensors:
+        return
+    first = tensors[0].device
+    if first.type != "cuda":
+        raise ValueError("Tensors must be on GPU")
+    if any(t.device != first for t in tensors[1:]):
+        raise ValueError("Tensors must be on same device")
+
+
+def validate_shape(tensor: Tensor, expected_shape, name: str = "Tensor") -> None:
+    if not validation_enabled():
+        return
+    expected = tuple(torch.Size(expected_shape))
+    if tuple(tensor.shape) != expected:
+        raise ValueError(f"{name} shape {tuple(tensor.shape)} doesn't match expected {expected}")
+
+
+def validate_layout_values(sparsity_layout: Tensor) -> None:
+    """Real dtype and only 0/1 entries (bool layouts need no device read)."""
+    if sparsity_layout.is_complex():
+        raise ValueError("Sparsity layout must not have a complex dtype")
+    if sparsity_layout.dtype == torch.bool:
+        return
+    if not bool(torch.all((sparsity_layout == 0) | (sparsity_layout == 1))):
+        raise ValueError("Sparsity layout values must be either 0 or 1")
+
+
+def validate_sparsity(sparsity_block_size: int, *pairs: tuple[Tensor, Tensor], counts=None) -> None:
+    """Checks compressed tensors against their layouts.
+
+    ``counts`` may give the already known number of active blocks per layout
+    (from a warm layout cache); otherwise the count is read from the device.
+    """
+    if not validation_enabled():
+        return
+    for i, (tensor, layout) in enumerate(pairs):
+        validate_layout_values(layout)
+        if tensor.device != layout.device:
+            raise ValueError("Tensor and sparsity layout must be on same device")
+        if not layout.is_contiguous():
+            raise ValueError("Sparsity layout must be contiguous")
+        if layout.dim() != 3:
+            raise ValueError("Sparsity layout must have exactly 3 dimensions")
+        if not (tensor.size(-1) == tensor.size(-2) == sparsity_block_size):
+            raise ValueError("Blocks not conforming to sparsity block size")
+        known = None if counts is None else counts[i]
+        n_active = int(torch.sum(layout.reshape(-1).to(torch.int))) if known is None else known
+        if tensor.size(0) != n_active:
+            raise ValueError("Mismatch between sparsity layout and blocks")
+
+
+def validate_sparsity_layout(*sparsity_layouts: Tensor) -> None:
+    if not validation_enabled():
+        return
+    for layout in sparsity_layouts:
+        validate_layout_values(layout)
+        if layout.dim() != 3:
+            raise ValueError("Sparsity layout must have exactly 3 dimensions")
+        if not layout.is_contiguous():
+            raise ValueError("Sparsity layout must be contiguous")
+        if layout.device.type != "cuda":
+            raise ValueError("Sparsity layout must be on GPU")
+
+
+def validate_sparsity_block_size(sparsity_block_size: int, *values) -> None:
+    if not validation_enabled():
+        return
+    if isinstance(sparsity_block_size, bool) or not isinstance(sparsity_block_size, int):
+        raise TypeError("Sparsity block size must be an integer")
+    if sparsity_block_size < 16:
+        raise ValueError("Sparsity block size must be at least 16")
+    if sparsity_block_size & (sparsity_block_size - 1):
+        raise ValueError("Sparsity block size must be a power of 2")
+    for value in values:
+        size = value if isinstance(value, (torch.Size, tuple, list)) else value.size()
+        if size[-1] % sparsity_block_size or size[-2] % sparsity_block_size:
+            raise ValueError("Tensor sizes must be divisible by sparsity block size")

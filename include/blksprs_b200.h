@@ -1,0 +1,209 @@
+/*
+ * blksprs_b200 — C ABI of the B200 (sm_100a) block-sparse matmul path.
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers, sizes and a
+ * CUDA stream handle (`void*`, a `cudaStream_t`), returns an `int` status
+ * (0 = BSP_OK) and never throws.  Unless stated otherwise nothing here
+ * allocates or frees device memory: the caller owns every buffer (inputs,
+ * outputs and the small workspaces whose sizes the `*_bytes` helpers report).
+ *
+ * Data model (identical to the blksprs library this path replaces):
+ *   compressed tensor   contiguous (n_blocks, bs, bs), fp16 / bf16 / fp32;
+ *                       block p is the p-th non-zero of the layout in
+ *                       row-major (batch, row, col) order.
+ *   sparsity layout     contiguous (B, rows/bs, cols/bs) of 0/1 in any real
+ *                       dtype (bool, integers, floats).
+ *   LUT                 int64 (n, 3) rows (batch, row, col) of the non-zeros
+ *                       (blksprs/utils/tools.py:33-35, build_layout_indices).
+ *   reverse LUT         int64 (B*R*C,): rank of the block among the non-zeros
+ *                       or -1 (blksprs/utils/tools.py:38-57,
+ *                       build_packed_indices).
+ */
+#ifndef BLKSPRS_B200_H
+#define BLKSPRS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+enum {
+    BSP_OK = 0,
+    BSP_ERR_INVALID_ARG = 1,   /* null pointer, negative size, bad enum          */
+    BSP_ERR_UNSUPPORTED = 2,   /* dtype / block size not handled by this build   */
+    BSP_ERR_WORKSPACE = 3,     /* workspace smaller than the *_bytes helper says */
+    BSP_ERR_CUDA = 4,          /* a CUDA runtime / driver call failed            */
+    BSP_ERR_DEVICE_RANGE = 5,  /* status word: a LUT / pair index out of range   */
+    BSP_ERR_DEVICE_TIMEOUT = 6 /* status word: a bounded device wait ran out     */
+};
+
+/* element type of a sparsity layout */
+enum {
+    BSP_L_BOOL = 0, /* torch.bool / uint8 */
+    BSP_L_I8 = 1,
+    BSP_L_I16 = 2,
+    BSP_L_I32 = 3,
+    BSP_L_I64 = 4,
+    BSP_L_F16 = 5,
+    BSP_L_BF16 = 6,
+    BSP_L_F32 = 7,
+    BSP_L_F64 = 8
+};
+
+/* element type of a compressed tensor */
+enum { BSP_F16 = 0, BSP_BF16 = 1, BSP_F32 = 2 };
+
+/* which block product a launch computes; A, B, O are compressed tensors */
+enum {
+    BSP_OP_NN = 0, /* O(r,c) = sum_t A(r,t)   * B(t,c)    forward  O  = X * Y    */
+    BSP_OP_NT = 1, /* O(r,c) = sum_t A(r,t)   * B(c,t)^T  backward dX = dO * Y^T */
+    BSP_OP_TN = 2  /* O(r,c) = sum_t A(t,r)^T * B(t,c)    backward dY = X^T * dO */
+};
+
+/* output-layout inference rule */
+enum { BSP_LAYOUT_EXACT = 0, BSP_LAYOUT_FAST = 1, BSP_LAYOUT_OUTER = 2 };
+
+/* kernel family selector for bsp_matmul */
+enum {
+    BSP_KERNEL_AUTO = 0, /* tcgen05 for 16-bit data and bs >= 64, mma.sync otherwise */
+    BSP_KERNEL_MMA = 1,  /* force the mma.sync kernel (any dtype, any bs)            */
+    BSP_KERNEL_UMMA = 2  /* force the tcgen05 kernel (error if not applicable)       */
+};
+
+/* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
+int bsp_version(void);
+
+/* Text for a status code. No reference counterpart (the reference raises
+ * Python exceptions only; the host shim maps codes to those exceptions). */
+const char* bsp_status_string(int status);
+
+/* Text of the last CUDA error seen by the calling thread ("" if none). */
+const char* bsp_last_cuda_error(void);
+
+/* ---- LUT construction -------------------------------------------------- */
+
+/* Bytes of scratch the two LUT builders need for a layout of `numel` entries. */
+size_t bsp_lut_workspace_bytes(int64_t numel);
+
+/* Reverse LUT.  Replaces build_packed_indices, blksprs/utils/tools.py:38-57:
+ *   flat = layout.reshape(-1).to(int64)
+ *   packed[e] = (flat[e] == 1) ? cumsum(flat)[e] - 1 : -1
+ * `total_out` (device, int64[1], may be null) receives cumsum(flat)[-1]
+ * (0 for an empty layout). */
+int bsp_build_packed_indices(const void* layout, int layout_dtype, int64_t numel,
+                             int64_t* packed_out, int64_t* total_out,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+/* Number of non-zero layout entries, written to `count_out` (device int64[1]).
+ * Replaces the count in matmul_build_layout_cache, blksprs/ops/matmul.py:270-273
+ * (`torch.sum(layout.to(torch.int)).item()`), minus the host read, which the
+ * caller does.  Leaves per-chunk partial counts in `workspace` for
+ * bsp_build_layout_indices. */
+int bsp_count_nonzero(const void* layout, int layout_dtype, int64_t numel,
+                      int64_t* count_out, void* workspace, size_t workspace_bytes,
+                      void* stream);
+
+/* LUT.  Replaces build_layout_indices, blksprs/utils/tools.py:33-35
+ * (`torch.nonzero(layout).contiguous()`): row p of `lut_out` (int64, (n,3)) is
+ * the (batch,row,col) of the p-th non-zero in row-major order.  Must follow
+ * bsp_count_nonzero on the same layout, stream and workspace; `capacity_rows`
+ * is the number of rows `lut_out` can hold (rows beyond it are dropped). */
+int bsp_build_layout_indices(const void* layout, int layout_dtype,
+                             int64_t B, int64_t R, int64_t C,
+                             int64_t* lut_out, int64_t capacity_rows,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+/* Output-layout inference.  Replaces build_sparsity_layout_matmul (exact),
+ * _fast and _outer, blksprs/layouting/sparsity_layout.py:244-309.
+ * lx is (B,R,K), ly is (B,K,C), out is uint8/bool (B,R,C).
+ *   exact: out = any_k(lx[b,r,k] != 0 && ly[b,k,c] != 0)
+ *   fast : out = any_k(lx[b,r,k]) && any_k(ly[b,k,c])
+ *   outer: out = any_k(lx[b,r,k]) || any_k(ly[b,k,c])            */
+int bsp_layout_matmul(const void* lx, int lx_dtype, const void* ly, int ly_dtype,
+                      int64_t B, int64_t R, int64_t K, int64_t C, int mode,
+                      uint8_t* out, void* stream);
+
+/* ---- pair plan ---------------------------------------------------------
+ * The reference kernel walks all K/T segments of every output block and
+ * tests two reverse-LUT entries per step (blksprs/ops/matmul.py:191-226).
+ * Here that walk is done once per layout triple: for every output block p
+ * the plan stores the list of (a_block, b_block) index pairs it contracts.
+ *
+ * Indexing: for output block (b, r, c) and inner index t in [0, T)
+ *   a = packed_a[b*a_sb + r*a_sr + t*a_st],  b = packed_b[b*b_sb + t*b_st + c*b_sc]
+ * and the pair is kept iff both are >= 0.
+ */
+
+/* counts_out[p] (int32, n_out) = number of pairs of output block p. */
+int bsp_plan_count(const int64_t* lut_out, int64_t n_out,
+                   const int64_t* packed_a, int64_t a_sb, int64_t a_sr, int64_t a_st,
+                   const int64_t* packed_b, int64_t b_sb, int64_t b_st, int64_t b_sc,
+                   int64_t T, int32_t* counts_out, void* stream);
+
+/* Bytes of scratch bsp_plan_offsets needs. */
+size_t bsp_plan_workspace_bytes(int64_t n_out);
+
+/* offsets_out (int32, n_out+1) = exclusive prefix sum of counts; the last
+ * entry is the total pair count.  `total_out` (device int64[1], may be null)
+ * receives the same total in 64 bits so the caller can reject plans whose
+ * pair count does not fit int32. */
+int bsp_plan_offsets(const int32_t* counts, int64_t n_out, int32_t* offsets_out,
+                     int64_t* total_out, void* workspace, size_t workspace_bytes,
+                     void* stream);
+
+/* pairs_out (int32, (total,2)) filled in output-block order, t ascending. */
+int bsp_plan_fill(const int64_t* lut_out, int64_t n_out,
+                  const int64_t* packed_a, int64_t a_sb, int64_t a_sr, int64_t a_st,
+                  const int64_t* packed_b, int64_t b_sb, int64_t b_st, int64_t b_sc,
+                  int64_t T, const int32_t* offsets, int32_t* pairs_out, void* stream);
+
+/* Splits the n_out output blocks into `n_chunks` contiguous ranges of nearly
+ * equal cost (cost of a block = its pair count + `block_cost`);
+ * chunk_begin_out is int32 (n_chunks+1). */
+int bsp_plan_schedule(const int32_t* offsets, int64_t n_out, int32_t block_cost,
+                      int32_t n_chunks, int32_t* chunk_begin_out, void* stream);
+
+/* ---- block-sparse matmul ---------------------------------------------- */
+
+/* Number of persistent CTAs bsp_matmul launches for the tcgen05 kernel on the
+ * current device (= the `n_chunks` a schedule for it must have); 0 when
+ * the (dtype, bs) pair is served by the mma.sync kernel. */
+int bsp_matmul_num_chunks(int dtype, int bs, int kernel);
+
+/* Block-sparse product on a pair plan.  Replaces matmul_forward + matmul_kernel,
+ * blksprs/ops/matmul.py:70-127,148-253 (op = BSP_OP_NN), and the two products
+ * of matmul_wrapper_backward, blksprs/ops/matmul.py:130-145 (BSP_OP_NT,
+ * BSP_OP_TN), without materialising the transposes of ops/transpose.py.
+ *   a, b       compressed operands (n_a, bs, bs), (n_b, bs, bs) of `dtype`
+ *   out        compressed result (n_out, bs, bs) of `dtype`; every block is
+ *              written (zeros where a block has no pair); fp32 accumulation
+ *   offsets    int32 (n_out+1), pairs int32 (total,2)
+ *   chunk_begin int32 (n_chunks+1) from bsp_plan_schedule (tcgen05 kernel
+ *              only; may be null for the mma.sync kernel)
+ *   status_word device int32[1] or null: receives BSP_ERR_DEVICE_* when a
+ *              kernel meets an out-of-range index or a wait limit; never
+ *              cleared by the kernel. */
+int bsp_matmul(const void* a, int64_t n_a, const void* b, int64_t n_b,
+               void* out, int64_t n_out,
+               const int32_t* offsets, const int32_t* pairs,
+               const int32_t* chunk_begin, int32_t n_chunks,
+               int bs, int dtype, int op, int kernel,
+               int32_t* status_word, void* stream);
+
+/* Compressed transpose.  Replaces transpose_forward + flow_pull_kernel,
+ * blksprs/ops/transpose.py:45-51, blksprs/ops/flow.py:64-111:
+ *   out[p] = x[src_index[p]]^T  for p in [0, n_out), where src_index (int64,
+ * n_out) is packed_indices(layout) gathered at the transposed coordinates of
+ * the p-th non-zero of the transposed layout; out[p] = 0 when src_index[p] < 0.
+ * elem_bytes is 1, 2, 4 or 8. */
+int bsp_transpose_blocks(const void* x, int64_t n_x, void* out, int64_t n_out,
+                         const int64_t* src_index, int bs, int elem_bytes,
+                         void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BLKSPRS_B200_H */
