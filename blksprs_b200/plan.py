@@ -12,6 +12,7 @@ cache next to the reference-visible LUT entries:
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -111,8 +112,22 @@ def check_device_status(device: torch.device | None = None) -> None:
         raise _cabi.NativeError(code, "device status word")
 
 
-def run_pair_plan(plan: PairPlan, a: Tensor, b: Tensor, bs: int, kernel: int = _cabi.KERNEL_AUTO) -> Tensor:
+_KERNEL_NAMES = {"auto": _cabi.KERNEL_AUTO, "mma": _cabi.KERNEL_MMA, "umma": _cabi.KERNEL_UMMA}
+_kernel_choice = _KERNEL_NAMES[os.environ.get("BLKSPRS_B200_KERNEL", "auto")]
+
+
+def set_kernel(name: str) -> None:
+    """Selects the kernel family for later launches: ``"auto"`` (tcgen05 where it applies, else
+    mma.sync), ``"mma"`` or ``"umma"``.  Meant for tests and profiling; both families are sm_100a
+    CUDA kernels of the same library."""
+    global _kernel_choice
+    _kernel_choice = _KERNEL_NAMES[name]
+
+
+def run_pair_plan(plan: PairPlan, a: Tensor, b: Tensor, bs: int, kernel: int | None = None) -> Tensor:
     """Launches one block-sparse product on ``plan``; returns the compressed result ``(n_out, bs, bs)``."""
+    if kernel is None:
+        kernel = _kernel_choice
     device = a.device
     out = torch.empty((plan.n_out, bs, bs), dtype=a.dtype, device=device)
     if plan.n_out == 0:

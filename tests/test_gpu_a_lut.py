@@ -1,0 +1,119 @@
+"""LUT, reverse LUT and inferred layouts from the CUDA library: bit-exact against the reference vectors."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+from gpu_util import DEV
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name,layout", cases.lut_layouts(), ids=[n for n, _ in cases.lut_layouts()])
+def test_luts_bit_exact(golden, name, layout):
+    from blksprs_b200.utils import tools
+    dev = layout.to(DEV)
+    lut = tools.build_layout_indices(dev)
+    packed = tools.build_packed_indices(dev)
+    assert type(lut) is torch.Tensor and lut.dtype == torch.int64 and lut.is_contiguous()
+    assert packed.dtype == torch.int64 and packed.dim() == 1
+    assert np.array_equal(lut.cpu().numpy(), golden[f"lut/{name}/layout_indices"])
+    assert np.array_equal(packed.cpu().numpy(), golden[f"lut/{name}/packed_indices"])
+    assert tools.count_active_blocks(dev) == int(golden[f"lut/{name}/n_sparse_blocks"])
+
+
+def test_luts_bfloat16_layout():
+    from blksprs_b200.utils import tools
+    layout = cases.bernoulli_layout((3, 9, 11), 0.4, 50)
+    dev = layout.to(torch.bfloat16).to(DEV)
+    assert np.array_equal(tools.build_layout_indices(dev).cpu().numpy(), oracle.layout_indices(layout))
+    assert np.array_equal(tools.build_packed_indices(dev).cpu().numpy(), oracle.packed_indices(layout))
+
+
+@pytest.mark.parametrize("name,lx,ly", cases.layout_pairs(), ids=[n for n, _, _ in cases.layout_pairs()])
+def test_layout_inference_bit_exact(golden, name, lx, ly):
+    import blksprs_b200 as bs
+    for fn, key in ((bs.layouting.build_sparsity_layout_matmul, "exact"),
+                    (bs.layouting.build_sparsity_layout_matmul_fast, "fast"),
+                    (bs.layouting.build_sparsity_layout_matmul_outer, "outer")):
+        got = fn(lx.to(DEV), ly.to(DEV))
+        assert type(got) is torch.Tensor and got.dtype == torch.bool
+        assert np.array_equal(got.cpu().numpy(), golden[f"infer/{name}/{key}"]), key
+
+
+def test_benchmark_layouts_bit_exact(golden):
+    """Config-2 sized layouts: LUT digests recorded from the reference."""
+    import hashlib
+    import blksprs_b200 as bs
+    from blksprs_b200.ops.matmul import matmul_build_layout_cache
+
+    def digest(t):
+        return hashlib.sha256(t.contiguous().cpu().numpy().tobytes()).hexdigest()
+
+    for name, lx, ly in cases.big_layout_pairs():
+        lx, ly = lx.to(DEV), ly.to(DEV)
+        lo = bs.layouting.build_sparsity_layout_matmul(lx, ly)
+        cache = matmul_build_layout_cache(None, lx, ly, lo)
+        got = [digest(cache["packed_indices_x"]), digest(cache["packed_indices_y"]),
+               digest(cache["layout_indices_o"]), digest(lo.to(torch.uint8))]
+        assert got == list(golden[f"big/{name}/digest"])
+        assert cache["n_sparse_blocks"] == int(golden[f"big/{name}/n_sparse_blocks"])
+
+
+def test_exact_layout_is_subset_of_fast():
+    """test/cases/test_blocksparse.py:1011-1022."""
+    import blksprs_b200 as bs
+    lx = cases.bernoulli_layout((4, 16, 12), 0.2, 51).to(DEV)
+    ly = cases.bernoulli_layout((4, 12, 20), 0.2, 52).to(DEV)
+    exact = bs.layouting.build_sparsity_layout_matmul(lx, ly)
+    fast = bs.layouting.build_sparsity_layout_matmul_fast(lx, ly)
+    outer = bs.layouting.build_sparsity_layout_matmul_outer(lx, ly)
+    assert bool(torch.all(fast | ~exact)) and bool(torch.all(outer | ~fast))
+
+
+def test_large_layout_helpers():
+    """4096 x 512 x 1 layouts (test/cases/test_blocksparse.py:2523-2549), against the oracle."""
+    import blksprs_b200 as bs
+    lx = cases.bernoulli_layout((64, 512, 1), 0.5, 53)
+    ly = cases.bernoulli_layout((64, 1, 4), 0.5, 54)
+    for fn, ofn in ((bs.layouting.build_sparsity_layout_matmul, oracle.layout_matmul),
+                    (bs.layouting.build_sparsity_layout_matmul_fast, oracle.layout_matmul_fast),
+                    (bs.layouting.build_sparsity_layout_matmul_outer, oracle.layout_matmul_outer)):
+        assert np.array_equal(fn(lx.to(DEV), ly.to(DEV)).cpu().numpy(), ofn(lx, ly))
+
+
+def test_pair_plan_matches_oracle():
+    from blksprs_b200.ops.matmul import matmul_build_layout_cache, _backward_plans, _PLANS
+    lx = cases.bernoulli_layout((3, 7, 9), 0.4, 55)
+    ly = cases.bernoulli_layout((3, 9, 5), 0.4, 56)
+    lo = cases.bernoulli_layout((3, 7, 5), 0.6, 57)
+    cache = matmul_build_layout_cache(None, lx.to(DEV), ly.to(DEV), lo.to(DEV))
+    plans = cache[_PLANS]
+    _backward_plans(plans, cache["packed_indices_x"], cache["packed_indices_y"], int(lx.sum()), int(ly.sum()))
+    px = oracle.packed_indices(lx).reshape(lx.shape)
+    py = oracle.packed_indices(ly).reshape(ly.shape)
+    po = oracle.packed_indices(lo).reshape(lo.shape)
+
+    def expect(lut, fa, fb, T):
+        offs, pairs = [0], []
+        for b, r, c in lut:
+            for t in range(T):
+                ia, ib = fa(b, r, c, t), fb(b, r, c, t)
+                if ia >= 0 and ib >= 0:
+                    pairs.append((ia, ib))
+            offs.append(len(pairs))
+        return np.array(offs), np.array(pairs).reshape(-1, 2)
+
+    checks = [
+        (plans.forward, oracle.layout_indices(lo), lambda b, i, j, t: px[b, i, t], lambda b, i, j, t: py[b, t, j], 9),
+        (plans.grad_x, oracle.layout_indices(lx), lambda b, i, k, t: po[b, i, t], lambda b, i, k, t: py[b, k, t], 5),
+        (plans.grad_y, oracle.layout_indices(ly), lambda b, k, j, t: px[b, t, k], lambda b, k, j, t: po[b, t, j], 7),
+    ]
+    for plan, lut, fa, fb, T in checks:
+        offs, pairs = expect(lut, fa, fb, T)
+        assert np.array_equal(plan.offsets.cpu().numpy(), offs)
+        assert plan.n_pairs == len(pairs)
+        assert np.array_equal(plan.pairs.cpu().numpy()[:plan.n_pairs], pairs)
+        cb = plan.chunk_begin.cpu().numpy()
+        assert cb[0] == 0 and cb[-1] == plan.n_out and np.all(np.diff(cb) >= 0)
