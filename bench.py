@@ -190,7 +190,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.02)
+            self._stop.wait(0.005)
 
     def __enter__(self):
         if self._nv is not None:
@@ -275,6 +275,57 @@ def run_reference_arm(args):
 # GPU arm
 # ---------------------------------------------------------------------------------------------
 
+def run_triton_arm(args):
+    """Times the reference's own Triton op (installed under baseline/_ref) on the same workload:
+    ``bs.ops.matmul`` forward + ``backward`` with a warm ``layout_cache``, DEFAULT autotune profile."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    line = {"impl": "triton-reference", "metric": METRIC, "unit": "TFLOP/s"}
+    try:
+        sys.path.insert(0, ref_dir)
+        os.environ.setdefault("BLKSPRS_AUTOTUNE", "DEFAULT")
+        import blksprs as ref
+    except Exception as exc:  # not installed on this box
+        line["unavailable"] = f"reference not importable from baseline/_ref: {exc!r}"[:200]
+        print(json.dumps(line), flush=True)
+        return
+    dev = torch.device("cuda", 0)
+    lx, ly, lo, bsz, dtype = workload_layouts(args.config)
+    wm = work_model(lx, ly, lo, bsz, torch.empty((), dtype=dtype).element_size())
+    lxd, lyd, lod = lx.to(dev), ly.to(dev), lo.to(dev)
+    sets = [workload_values(args.config, lx, ly, lo, bsz, dtype, seed=s, device=dev) for s in range(N_BUFFER_SETS)]
+    results = {}
+    for label, validate in (("validation_on", True), ("validation_off", False)):
+        (ref.utils.enable_validation if validate else ref.utils.disable_validation)()
+        cache = {}
+
+        def step(i, fwd_only=False):
+            x, y, g = sets[i % N_BUFFER_SETS]
+            x = x.detach().requires_grad_(not fwd_only)
+            y = y.detach().requires_grad_(not fwd_only)
+            out = ref.ops.matmul(x, lxd, y, lyd, lod, bsz, cache)
+            if not fwd_only:
+                out.backward(g)
+            return out
+
+        for mode, flops in (("fwd", wm["flops"]["fwd"]), ("fwd_bwd", sum(wm["flops"].values()))):
+            for i in range(max(args.warmup, 3)):
+                step(i, mode == "fwd")
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for i in range(args.steps):
+                step(i, mode == "fwd")
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            results[f"{label}/{mode}"] = {"ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12}
+    ref.utils.enable_validation()
+    line.update({"value": results["validation_off/fwd_bwd"]["tflops"], "results": results,
+                 "config": {"workload": args.config}, "steps": args.steps, "warmup": args.warmup,
+                 "triton": __import__("triton").__version__})
+    print(json.dumps(line), flush=True)
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -309,7 +360,7 @@ def run_gpu_arm(args):
         x, y, g = workload_values(args.config, lx, ly, lo, bsz, dtype, seed=s + 10 * rank, device=dev)
         sets.append((x, y, g))
 
-    cache = matmul_build_layout_cache({}, lxd, lyd, lod)
+    cache = matmul_build_layout_cache({}, lxd, lyd, lod, bsz)
     plans = cache[_PLANS]
     _backward_plans(plans, cache["packed_indices_x"], cache["packed_indices_y"], sets[0][0].size(0),
                     sets[0][1].size(0))
@@ -377,12 +428,13 @@ def run_gpu_arm(args):
             dst.copy_(src, non_blocking=True)
         torch.cuda.synchronize()
 
-    for i in range(min(args.warmup, 3)):
+    e2e_steps = 0 if args.kernel_only else args.steps
+    for i in range(min(args.warmup, 3) if e2e_steps else 0):
         e2e_step(i)
     g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     g0.record()
-    for i in range(args.steps):
+    for i in range(e2e_steps):
         e2e_step(i)
     g1.record()
     barrier()
@@ -401,7 +453,7 @@ def run_gpu_arm(args):
     if rank == 0:
         peaks = measured_peaks()
         value = flops_all * args.steps / (ms * 1e-3) / 1e12
-        e2e_value = flops_all * args.steps / (e2e_ms * 1e-3) / 1e12
+        e2e_value = flops_all * e2e_steps / (e2e_ms * 1e-3) / 1e12 if e2e_steps else None
         fwd_bytes = wm["bytes"]["fwd"]
         achieved = fwd_bytes / (fwd_ms * 1e-3) / 1e9
         line = {
@@ -423,11 +475,11 @@ def run_gpu_arm(args):
                 "traffic": FWD_KERNEL_DRAM_TRAFFIC_BYTES,
             },
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / args.steps},
+                    "ms_per_step": e2e_ms / max(e2e_steps, 1)},
             "gpu_launches": 3 * args.steps,
             "clocks": clocks.summary(),
         }
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not args.kernel_only:
             sample = min(lx.size(0), args.cpu_batch)
             dt, cflops = cpu_step_time(args.config, sample, 2, 1)
             line["cpu_baseline"] = {"value": cflops / dt / 1e12, "unit": "TFLOP/s",
@@ -441,15 +493,19 @@ def run_gpu_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--config", default="config2")
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "triton"])
     ap.add_argument("--cpu-batch", type=int, default=16, help="batches of the workload the CPU arm times")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end and CPU legs (for short profiler runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.impl == "triton":
+        run_triton_arm(args)
     else:
         run_gpu_arm(args)
 

@@ -193,6 +193,7 @@ plan_walk_kernel(const int64_t* __restrict__ lut_out, int64_t n_out,
         const int64_t* pb = packed_b + b * b_sb + c * b_sc;
         int32_t n = 0;
         const int32_t base = FILL ? offsets[p] : 0;
+        const int32_t last = FILL ? offsets[p + 1] - 1 : -1;  // position of the block's last pair
         for (int64_t t0 = 0; t0 < T; t0 += 32) {
             const int64_t t = t0 + lane;
             int64_t ia = -1, ib = -1;
@@ -204,7 +205,7 @@ plan_walk_kernel(const int64_t* __restrict__ lut_out, int64_t n_out,
             const unsigned m = __ballot_sync(0xffffffffu, hit);
             if (FILL && hit) {
                 const int32_t pos = base + n + __popc(m & ((1u << lane) - 1u));
-                pairs[2 * (int64_t)pos + 0] = (int32_t)ia;
+                pairs[2 * (int64_t)pos + 0] = (int32_t)ia | (pos == last ? 0x40000000 : 0);
                 pairs[2 * (int64_t)pos + 1] = (int32_t)ib;
             }
             n += __popc(m);

@@ -131,7 +131,7 @@ matmul_mma_kernel(const T* __restrict__ a, int64_t n_a, const T* __restrict__ b,
     // copies nothing) when the pair's indices are out of range.
     auto issue = [&](int s, int buf) -> bool {
         const int pr = beg + s / nkc, kc = s % nkc;
-        const int ia = pairs[2 * (int64_t)pr], ib = pairs[2 * (int64_t)pr + 1];
+        const int ia = pairs[2 * (int64_t)pr] & 0x3fffffff, ib = pairs[2 * (int64_t)pr + 1];
         const bool ok = ia >= 0 && ia < n_a && ib >= 0 && ib < n_b;
         if (ok) {
             const int ar0 = A_TRANS ? kc * TILE : tm * TILE, ac0 = A_TRANS ? tm * TILE : kc * TILE;

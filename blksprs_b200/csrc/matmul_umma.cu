@@ -34,18 +34,46 @@ namespace {
 
 constexpr int kThreads = 192;
 constexpr uint32_t kFlagLast = 1u;  // stage holds the last pair of its output block
+constexpr int kPairLastBit = 0x40000000;   // set on pairs[2p] when p is the last pair of its block
+constexpr int kPairIndexMask = 0x3fffffff;
 constexpr unsigned long long kWaitLimitNs = 1000000000ull;
 
+#ifdef BSP_UMMA_PROFILE
+// Debug build only: per-CTA cycle counters (8 per CTA) read back by bsp_debug_read_prof.
+__device__ long long g_prof[1024 * 8];
+#define PROF_DECL(name) long long name = 0
+#define PROF_T0(t) long long t = clock64()
+#define PROF_ADD(acc, t) acc += clock64() - t
+#define PROF_STORE(i, v) g_prof[blockIdx.x * 8 + (i)] = (v)
+#else
+#define PROF_DECL(name)
+#define PROF_T0(t)
+#define PROF_ADD(acc, t)
+#define PROF_STORE(i, v)
+#endif
+
 template <int BS> struct Cfg;
+#ifndef BSP_UMMA64_STAGES
+#define BSP_UMMA64_STAGES 4
+#endif
+#ifndef BSP_UMMA64_CTAS
+#define BSP_UMMA64_CTAS 3
+#endif
+#ifndef BSP_UMMA64_ACCS
+#define BSP_UMMA64_ACCS 2
+#endif
+
 template <> struct Cfg<64> {
-    static constexpr int kStages = 8;     // 8 x 16 KiB
-    static constexpr int kAccs = 4;       // 4 x 64 columns
-    static constexpr int kTmemCols = 256;
+    static constexpr int kStages = BSP_UMMA64_STAGES;  // x 16 KiB
+    static constexpr int kAccs = BSP_UMMA64_ACCS;      // x 64 columns
+    static constexpr int kTmemCols = 64 * BSP_UMMA64_ACCS;
+    static constexpr int kCtasPerSm = BSP_UMMA64_CTAS;
 };
 template <> struct Cfg<128> {
     static constexpr int kStages = 3;     // 3 x 64 KiB
     static constexpr int kAccs = 4;       // 4 x 128 columns
     static constexpr int kTmemCols = 512;
+    static constexpr int kCtasPerSm = 1;
 };
 
 template <int BS>
@@ -140,6 +168,11 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
           "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void st_global_32B(void* p, const uint32_t* u) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"l"(p), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7])
+                 : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), sm_100
@@ -181,7 +214,7 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t base, int kstep) {
 }
 
 template <typename T, int BS, int OP>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, Cfg<BS>::kCtasPerSm)
 matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    int64_t n_a, int64_t n_b, T* __restrict__ out,
                    const int32_t* __restrict__ offsets, const int32_t* __restrict__ pairs,
@@ -239,82 +272,85 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
         if (warp == 0) {
             // ---------------- producer ----------------
+            // Pairs are handled in rounds of S: in a round lane l (< S) owns pair p0 + l and ring
+            // stage l.  Each lane polls its own stage's "empty" barrier and issues its two block
+            // copies as soon as that stage is free, so up to S copies are issued per instruction.
             const int2* pairs2 = reinterpret_cast<const int2*>(pairs);
-            int stage = 0;
             uint32_t phase = 0;
-            int blk = blk_begin;
-            // window of block end offsets: lane l holds offsets[win + l + 1]
-            int win = blk_begin;
-            auto load_window = [&](int w) -> int {
-                const int i = w + lane + 1;
-                return i <= blk_end ? offsets[i] : 0x7fffffff;
-            };
-            int win_cur = load_window(win);
-            int win_nxt = load_window(win + 32);
-            auto load_batch = [&](int p0) -> int2 {
+            auto load_round = [&](int p0) -> int2 {
                 const int i = p0 + lane;
-                return i < pr_end ? pairs2[i] : make_int2(0, 0);
+                return (lane < S && i < pr_end) ? pairs2[i] : make_int2(0, 0);
             };
-            int2 batch_cur = load_batch(pr_begin);
+            int2 cur = load_round(pr_begin);
             bool alive = true;
-            for (int p0 = pr_begin; p0 < pr_end && alive; p0 += 32) {
-                const int2 batch_nxt = load_batch(p0 + 32);
-                const int m = min(32, pr_end - p0);
-                for (int j = 0; j < m && alive; ++j) {
-                    const int pr = p0 + j;
-                    int ia = __shfl_sync(0xffffffffu, batch_cur.x, j);
-                    int ib = __shfl_sync(0xffffffffu, batch_cur.y, j);
-                    // advance the block cursor to the block that owns pair `pr`
-                    int cur_end;
-                    for (;;) {
-                        if (blk - win >= 32) {
-                            win += 32;
-                            win_cur = win_nxt;
-                            win_nxt = load_window(win + 32);
-                        }
-                        cur_end = __shfl_sync(0xffffffffu, win_cur, blk - win);
-                        if (cur_end > pr) break;
-                        ++blk;
+            PROF_DECL(w_empty);
+            PROF_T0(t_start);
+            for (int p0 = pr_begin; p0 < pr_end && alive; p0 += S) {
+                const int2 nxt = load_round(p0 + S);
+                if (lane < S && p0 + lane < pr_end) {
+                    int ia = cur.x & kPairIndexMask, ib = cur.y;
+                    const uint32_t last = (cur.x & kPairLastBit) ? kFlagLast : 0u;
+                    if (ia >= n_a || ib < 0 || ib >= n_b) {
+                        if (status_word) *status_word = BSP_ERR_DEVICE_RANGE;
+                        ia = 0;
+                        ib = 0;
                     }
-                    if (lane == 0) {
-                        if (ia < 0 || ia >= n_a || ib < 0 || ib >= n_b) {
-                            if (status_word) *status_word = BSP_ERR_DEVICE_RANGE;
-                            ia = 0;
-                            ib = 0;
-                        }
-                        if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status_word)) {
-                            alive = false;
-                        } else {
-                            // the MMA thread starts a new accumulator after each "last" pair
-                            flags[stage] = (pr + 1 == cur_end) ? kFlagLast : 0u;
-                            const uint32_t sa = data + stage * L::kStageBytes;
-                            const uint32_t sb = sa + L::kBlockBytes;
-                            const uint32_t bar = full_bar + 8 * stage;
-                            armed[stage] = (int)phase;
-                            mbar_arrive_expect_tx(bar, L::kStageBytes);
+                    const uint32_t ebar = empty_bar + 8 * lane;
+                    const uint32_t fbar = full_bar + 8 * lane;
+                    const uint32_t sa = data + lane * L::kStageBytes;
+                    const uint32_t sb = sa + L::kBlockBytes;
+                    PROF_T0(tw);
+                    unsigned long long t0 = 0;
+                    for (uint32_t spins = 1;; ++spins) {
+                        if (mbar_try_wait(ebar, phase ^ 1u)) {
+                            flags[lane] = last;
+                            armed[lane] = (int)phase;
+                            mbar_arrive_expect_tx(fbar, L::kStageBytes);
 #pragma unroll
                             for (int h = 0; h < BS / 64; ++h) {
-                                tma_load_2d(sa + h * (BS * 128), &map_a, h * 64, ia * BS, bar);
-                                tma_load_2d(sb + h * (BS * 128), &map_b, h * 64, ib * BS, bar);
+                                tma_load_2d(sa + h * (BS * 128), &map_a, h * 64, ia * BS, fbar);
+                                tma_load_2d(sb + h * (BS * 128), &map_b, h * 64, ib * BS, fbar);
+                            }
+                            break;
+                        }
+                        if ((spins & 0xff) == 0) {
+                            if (t0 == 0) t0 = global_timer();
+                            if (*abort_flag || global_timer() - t0 > kWaitLimitNs) {
+                                *abort_flag = 1;
+                                if (status_word) *status_word = BSP_ERR_DEVICE_TIMEOUT;
+                                alive = false;
+                                break;
                             }
                         }
                     }
-                    alive = __shfl_sync(0xffffffffu, (int)alive, 0) != 0;
-                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                    PROF_ADD(w_empty, tw);
                 }
-                batch_cur = batch_nxt;
+                alive = __all_sync(0xffffffffu, alive);
+                phase ^= 1u;
+                cur = nxt;
+            }
+            if (lane == 0) {
+                PROF_STORE(0, clock64() - t_start);
+                PROF_STORE(1, w_empty);
             }
         } else if (warp == 1) {
             // ---------------- MMA issuer ----------------
             if (lane == 0) {
                 int stage = 0, acc = 0;
                 uint32_t phase = 0, acc_phase = 0;
-                bool first = true, alive = true;
-                for (int pr = pr_begin; pr < pr_end && alive; ++pr) {
+                bool first = true;
+                PROF_DECL(w_full);
+                PROF_DECL(w_tempty);
+                PROF_T0(t_start);
+                for (int pr = pr_begin; pr < pr_end; ++pr) {
                     if (first) {
+                        PROF_T0(tw);
                         if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, status_word)) break;
+                        PROF_ADD(w_tempty, tw);
                     }
+                    PROF_T0(tw2);
                     if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status_word)) break;
+                    PROF_ADD(w_full, tw2);
                     tc_fence_after();
                     const uint32_t fl = flags[stage];
                     const uint32_t sa = data + stage * L::kStageBytes;
@@ -335,6 +371,9 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     if (++stage == S) { stage = 0; phase ^= 1u; }
                 }
                 // make sure no MMA is still running before tensor memory is freed
+                PROF_STORE(2, clock64() - t_start);
+                PROF_STORE(3, w_full);
+                PROF_STORE(4, w_tempty);
                 tc_commit(drain_bar);
                 mbar_wait(drain_bar, 0, abort_flag, status_word);
             }
@@ -347,6 +386,8 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             int acc = 0;
             uint32_t acc_phase = 0;
             bool alive = true;
+            PROF_DECL(w_tfull);
+            PROF_T0(t_start);
             for (int w0 = blk_begin; w0 < blk_end && alive; w0 += 32) {
                 const int bi = w0 + lane;
                 const int my_n = bi < blk_end ? offsets[bi + 1] - offsets[bi] : 0;
@@ -361,9 +402,11 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         for (int i = lane; i < VECS; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
                         continue;
                     }
+                    PROF_T0(tw);
                     if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, status_word)) {
                         alive = false;
                     }
+                    PROF_ADD(w_tfull, tw);
                     alive = __all_sync(0xffffffffu, alive);
                     if (!alive) break;
                     tc_fence_after();
@@ -374,15 +417,16 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         tc_ld32(taddr + c0, v);
                         tc_wait_ld();
                         if (row_valid) {
-                            uint4* dst = reinterpret_cast<uint4*>(o + (int64_t)row * BS + c0);
+                            // 32 columns = 64 bytes of the row: two 32-byte stores, each a whole sector
+                            T* dst = o + (int64_t)row * BS + c0;
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                uint4 u;
-                                u.x = pack2<T>(__uint_as_float(v[8 * i + 0]), __uint_as_float(v[8 * i + 1]));
-                                u.y = pack2<T>(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]));
-                                u.z = pack2<T>(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]));
-                                u.w = pack2<T>(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]));
-                                dst[i] = u;
+                            for (int i = 0; i < 2; ++i) {
+                                uint32_t u[8];
+#pragma unroll
+                                for (int e = 0; e < 8; ++e)
+                                    u[e] = pack2<T>(__uint_as_float(v[16 * i + 2 * e]),
+                                                    __uint_as_float(v[16 * i + 2 * e + 1]));
+                                st_global_32B(dst + 16 * i, u);
                             }
                         }
                     }
@@ -391,6 +435,11 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
                     if (++acc == A) { acc = 0; acc_phase ^= 1u; }
                 }
+            }
+            if (warp == 2 && lane == 0) {
+                PROF_STORE(5, clock64() - t_start);
+                PROF_STORE(6, w_tfull);
+                PROF_STORE(7, (long long)(pr_end - pr_begin) * 100000 + (blk_end - blk_begin));
             }
         }
     }
@@ -511,13 +560,19 @@ int launch_op(int op, const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a,
 
 }  // namespace
 
+#ifdef BSP_UMMA_PROFILE
+extern "C" int bsp_debug_read_prof(long long* host_out, int n) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_prof, sizeof(long long) * n);
+}
+#endif
+
 bool umma_applicable(int dtype, int bs) {
     return (dtype == BSP_F16 || dtype == BSP_BF16) && (bs == 64 || bs == 128);
 }
 
 int umma_num_chunks(int dtype, int bs) {
     if (!umma_applicable(dtype, bs)) return 0;
-    return num_sms();
+    return num_sms() * (bs == 64 ? Cfg<64>::kCtasPerSm : Cfg<128>::kCtasPerSm);
 }
 
 int launch_matmul_umma(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,

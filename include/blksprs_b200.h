@@ -154,7 +154,9 @@ int bsp_plan_offsets(const int32_t* counts, int64_t n_out, int32_t* offsets_out,
                      int64_t* total_out, void* workspace, size_t workspace_bytes,
                      void* stream);
 
-/* pairs_out (int32, (total,2)) filled in output-block order, t ascending. */
+/* pairs_out (int32, (total,2)) filled in output-block order, t ascending:
+ * pairs_out[2p] = a_block index, with bit 30 set on the last pair of its output
+ * block; pairs_out[2p+1] = b_block index.  Block indices must be below 2^30. */
 int bsp_plan_fill(const int64_t* lut_out, int64_t n_out,
                   const int64_t* packed_a, int64_t a_sb, int64_t a_sr, int64_t a_st,
                   const int64_t* packed_b, int64_t b_sb, int64_t b_st, int64_t b_sc,

@@ -114,6 +114,11 @@ def test_pair_plan_matches_oracle():
         offs, pairs = expect(lut, fa, fb, T)
         assert np.array_equal(plan.offsets.cpu().numpy(), offs)
         assert plan.n_pairs == len(pairs)
-        assert np.array_equal(plan.pairs.cpu().numpy()[:plan.n_pairs], pairs)
+        got = plan.pairs.cpu().numpy()[:plan.n_pairs]
+        assert np.array_equal(got & np.array([0x3fffffff, -1]), pairs)
+        # bit 30 of the a-index marks the last pair of every non-empty output block
+        last = np.zeros(len(pairs), dtype=bool)
+        last[offs[1:][np.diff(offs) > 0] - 1] = True
+        assert np.array_equal((got[:, 0] >> 30) & 1, last.astype(got.dtype))
         cb = plan.chunk_begin.cpu().numpy()
         assert cb[0] == 0 and cb[-1] == plan.n_out and np.all(np.diff(cb) >= 0)
