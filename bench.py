@@ -38,9 +38,9 @@ if ROOT not in sys.path:
 METRIC = "block-sparse matmul effective TFLOP/s (nnz-block FLOPs), forward+backward"
 N_BUFFER_SETS = 4
 
-# DRAM bytes (read + write) of one forward launch of the default workload, from the ncu capture
-# summarised in profiles/ (None until a capture exists).
-FWD_KERNEL_DRAM_TRAFFIC_BYTES = None
+# DRAM bytes (read + write) of one forward launch of the default workload (config2), from the ncu
+# capture summarised in profiles/matmul_umma_kernel_config2.md: 101.5 MB read + 82.7 MB written.
+FWD_KERNEL_DRAM_TRAFFIC_BYTES = {"config2": 184.2e6}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -472,7 +472,7 @@ def run_gpu_arm(args):
                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                 "peak_source": peaks["source"], "algorithmic_bytes": fwd_bytes, "ms_per_launch": fwd_ms,
                 "tensor_tflops": wm["flops"]["fwd"] / (fwd_ms * 1e-3) / 1e12,
-                "traffic": FWD_KERNEL_DRAM_TRAFFIC_BYTES,
+                "traffic": FWD_KERNEL_DRAM_TRAFFIC_BYTES.get(args.config),
             },
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / max(e2e_steps, 1)},
