@@ -14,7 +14,7 @@ import torch
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libblksprs_b200.so"
 
 # status codes (include/blksprs_b200.h)
-OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_RANGE, ERR_DEVICE_TIMEOUT = range(7)
+OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_RANGE, ERR_DEVICE_TIMEOUT, ERR_TOO_LARGE = range(8)
 # matmul ops / kernel selectors / layout modes
 OP_NN, OP_NT, OP_TN = 0, 1, 2
 KERNEL_AUTO, KERNEL_MMA, KERNEL_UMMA = 0, 1, 2
@@ -33,6 +33,8 @@ SIGNATURES = {
     "bsp_last_cuda_error": (c_char_p, []),
     "bsp_lut_workspace_bytes": (c_size_t, [c_int64]),
     "bsp_build_packed_indices": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "bsp_build_packed_indices_static": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
+    "bsp_static_scratch_max_numel": (c_int64, []),
     "bsp_count_nonzero": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),
     "bsp_build_layout_indices": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64,
                                          c_void_p, c_size_t, c_void_p]),

@@ -30,6 +30,7 @@ extern "C" const char* bsp_status_string(int status) {
         case BSP_ERR_CUDA: return "CUDA call failed";
         case BSP_ERR_DEVICE_RANGE: return "device: block index out of range";
         case BSP_ERR_DEVICE_TIMEOUT: return "device: bounded wait ran out";
+        case BSP_ERR_TOO_LARGE: return "size exceeds the limit of the built-in scratch array";
         default: return "unknown status";
     }
 }

@@ -4,6 +4,8 @@
 // three-phase (reduce, scan chunk sums, apply) prefix sum.
 #include <limits.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace bsp {
@@ -492,6 +494,58 @@ extern "C" int bsp_transpose_blocks(const void* x, int64_t n_x, void* out, int64
         case 8: transpose_blocks_kernel<uint64_t><<<grid, 256, 0, stream>>>((const uint64_t*)x, n_x, (uint64_t*)out, src_index, bs); break;
         default: return BSP_ERR_UNSUPPORTED;
     }
+    BSP_LAUNCH_CHECK();
+    return BSP_OK;
+}
+
+// ---- reverse LUT without caller-provided scratch --------------------------------------
+// The chunk sums of the scan live in a fixed array inside the library image instead of a
+// caller-allocated workspace.  Every GPU that loads the library carries the array
+// (16 KiB + 8 B) until the process exits.
+static constexpr int64_t kStaticMaxNumel = (int64_t)1 << 22;  // 4 194 304 layout entries
+static __device__ __align__(256) int64_t g_static_scan_scratch[kStaticMaxNumel / bsp::kScanChunk + 1];
+
+// Device address of the array on the current device.  The symbol's name is only a host-side
+// handle, so the address is looked up once per device (with that device current) and cached.
+static int static_scan_scratch(int64_t** out) {
+    static std::mutex mu;
+    static int64_t* cached[64] = {nullptr};
+    int dev = -1;
+    BSP_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return BSP_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cached[dev]) {
+        void* p = nullptr;
+        BSP_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scan_scratch));
+        if (!p) return BSP_ERR_CUDA;
+        cached[dev] = (int64_t*)p;
+    }
+    *out = cached[dev];
+    return BSP_OK;
+}
+
+extern "C" int64_t bsp_static_scratch_max_numel(void) { return kStaticMaxNumel; }
+
+extern "C" int bsp_build_packed_indices_static(const void* layout, int layout_dtype, int64_t numel,
+                                               int64_t* packed_out, int64_t* total_out, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (numel < 0 || (numel > 0 && (!layout || !packed_out))) return BSP_ERR_INVALID_ARG;
+    if (numel > kStaticMaxNumel) return BSP_ERR_TOO_LARGE;
+    int64_t* ws = nullptr;
+    int st = static_scan_scratch(&ws);
+    if (st != BSP_OK) return st;
+    // Nothing in the array has to start at zero: phase 1 writes chunk sums [0, nch), phase 2
+    // rewrites them in place and writes entry nch, phase 3 only reads what those two wrote.
+    const int64_t nch = scan_chunks(numel);
+    bool ok = dispatch_layout_dtype(layout_dtype, [&](auto tag) {
+        using T = decltype(tag);
+        if (nch > 0)
+            chunk_reduce_kernel<T, kViewI64><<<(unsigned)nch, kScanThreads, 0, stream>>>((const T*)layout, numel, ws);
+        chunk_scan_kernel<<<1, kScanThreads, 0, stream>>>(ws, nch, total_out);
+        if (nch > 0)
+            packed_apply_kernel<T><<<(unsigned)nch, kScanThreads, 0, stream>>>((const T*)layout, numel, ws, packed_out);
+    });
+    if (!ok) return BSP_ERR_UNSUPPORTED;
     BSP_LAUNCH_CHECK();
     return BSP_OK;
 }

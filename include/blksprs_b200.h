@@ -37,7 +37,8 @@ enum {
     BSP_ERR_WORKSPACE = 3,     /* workspace smaller than the *_bytes helper says */
     BSP_ERR_CUDA = 4,          /* a CUDA runtime / driver call failed            */
     BSP_ERR_DEVICE_RANGE = 5,  /* status word: a LUT / pair index out of range   */
-    BSP_ERR_DEVICE_TIMEOUT = 6 /* status word: a bounded device wait ran out     */
+    BSP_ERR_DEVICE_TIMEOUT = 6,/* status word: a bounded device wait ran out     */
+    BSP_ERR_TOO_LARGE = 7      /* input larger than a built-in scratch array     */
 };
 
 /* element type of a sparsity layout */
@@ -96,6 +97,38 @@ size_t bsp_lut_workspace_bytes(int64_t numel);
 int bsp_build_packed_indices(const void* layout, int layout_dtype, int64_t numel,
                              int64_t* packed_out, int64_t* total_out,
                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* Reverse LUT for callers that may not allocate device memory.  No counterpart
+ * in the reference (which allocates freely through torch); same result as
+ * bsp_build_packed_indices, bit for bit.
+ *
+ * Who needs it: hosts that hand out all device memory once at start-up from
+ * their own arena (an inference server that reserves the whole HBM for weights
+ * and KV cache, an embedded pipeline with a fixed memory map) and therefore
+ * have no allocator to ask for the scan's scratch buffer, and hosts for which
+ * the implicit device-wide synchronisation of cudaMalloc / cudaFree in the
+ * middle of a step is not acceptable.  Here the scratch is a fixed array inside
+ * the library image: 16 KiB + 8 B on every GPU that loads the library, held
+ * until the process exits.  The call itself, and everything it calls, performs
+ * no cudaMalloc, cudaFree or other allocating routine; `layout`, `packed_out`
+ * and `total_out` are still the caller's buffers.
+ *
+ * Limits and rules:
+ *  - numel <= bsp_static_scratch_max_numel() (4 194 304 layout entries);
+ *    larger layouts are refused with BSP_ERR_TOO_LARGE and nothing is launched.
+ *  - The first call on each device looks up the array's device address (with
+ *    that device current) and caches it; make that first call during set-up,
+ *    before any stream capture begins.
+ *  - All calls on a device share the one array, which keeps the previous call's
+ *    contents (nothing in it needs clearing: each call overwrites what it later
+ *    reads).  Two calls whose kernels can overlap on the GPU (different streams
+ *    without an ordering between them) race on it; keep calls on one stream or
+ *    order them with events. */
+int bsp_build_packed_indices_static(const void* layout, int layout_dtype, int64_t numel,
+                                    int64_t* packed_out, int64_t* total_out, void* stream);
+
+/* Largest `numel` bsp_build_packed_indices_static accepts.  No reference counterpart. */
+int64_t bsp_static_scratch_max_numel(void);
 
 /* Number of non-zero layout entries, written to `count_out` (device int64[1]).
  * Replaces the count in matmul_build_layout_cache, blksprs/ops/matmul.py:270-273
