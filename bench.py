@@ -340,7 +340,7 @@ def run_gpu_arm(args):
     import blksprs_b200 as bs
     from blksprs_b200 import _cabi
     from blksprs_b200.ops.matmul import matmul_build_layout_cache, _backward_plans, _PLANS
-    from blksprs_b200.plan import run_pair_plan, check_device_status
+    from blksprs_b200.plan import check_device_status
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -367,9 +367,9 @@ def run_gpu_arm(args):
 
     def kernel_step(i):
         x, y, g = sets[i % N_BUFFER_SETS]
-        out = run_pair_plan(plans.forward, x, y, bsz)
-        gx = run_pair_plan(plans.grad_x, g, y, bsz)
-        gy = run_pair_plan(plans.grad_y, x, g, bsz)
+        out = plans.forward.run(x, y, bsz)
+        gx = plans.grad_x.run(g, y, bsz)
+        gy = plans.grad_y.run(x, g, bsz)
         return out, gx, gy
 
     def barrier():
@@ -400,7 +400,7 @@ def run_gpu_arm(args):
     f0.record()
     for i in range(args.steps):
         x, y, _ = sets[i % N_BUFFER_SETS]
-        run_pair_plan(plans.forward, x, y, bsz)
+        plans.forward.run(x, y, bsz)
     f1.record()
     torch.cuda.synchronize()
     fwd_ms = f0.elapsed_time(f1) / args.steps

@@ -50,6 +50,15 @@ SIGNATURES = {
     "bsp_matmul_num_chunks": (c_int, [c_int, c_int, c_int]),
     "bsp_matmul": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                            c_int32, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "bsp_panel_width": (c_int, [c_int, c_int]),
+    "bsp_matmul_panel_num_chunks": (c_int, [c_int, c_int]),
+    "bsp_panel_count": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
+                                c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "bsp_panel_fill": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
+                               c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "bsp_matmul_panel": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                 c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int, c_int, c_int, c_void_p,
+                                 c_void_p]),
     "bsp_transpose_blocks": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),
 }
 

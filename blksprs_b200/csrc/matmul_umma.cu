@@ -27,8 +27,11 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "umma_common.cuh"
 
 namespace bsp {
+
+using namespace umma;
 
 namespace {
 
@@ -36,7 +39,6 @@ constexpr int kThreads = 192;
 constexpr uint32_t kFlagLast = 1u;  // stage holds the last pair of its output block
 constexpr int kPairLastBit = 0x40000000;   // set on pairs[2p] when p is the last pair of its block
 constexpr int kPairIndexMask = 0x3fffffff;
-constexpr unsigned long long kWaitLimitNs = 1000000000ull;
 
 #ifdef BSP_UMMA_PROFILE
 // Debug build only: per-CTA cycle counters (8 per CTA) read back by bsp_debug_read_prof.
@@ -87,115 +89,6 @@ struct SmemLayout {
     static constexpr int kMiscBytes = (2 * Cfg<BS>::kStages + 2) * 4;
     static constexpr int kTotal = kDataBytes + kBarBytes + kMiscBytes + 1024 /* alignment slack */;
 };
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ unsigned long long global_timer() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    return done != 0;
-}
-// Bounded wait: false if the limit ran out or another role already gave up.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                            int32_t* status_word) {
-    const unsigned long long t0 = global_timer();
-    for (uint32_t it = 1;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 0xff) == 0) {
-            if (*abort_flag) return false;
-            if (global_timer() - t0 > kWaitLimitNs) {
-                *abort_flag = 1;
-                if (status_word) *status_word = BSP_ERR_DEVICE_TIMEOUT;
-                return false;
-            }
-        }
-    }
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int32_t* status_word) {
-    if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_flag, status_word);
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
-                                            uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                           uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void st_global_32B(void* p, const uint32_t* u) {
-    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
-                 ::"l"(p), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7])
-                 : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), sm_100
-// descriptor version 1.  Offsets are in bytes; the fields drop the 4 LSBs.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
-    d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
-    d |= 1ull << 46;
-    d |= 2ull << 61;
-    return d;
-}
-
-template <typename T> __device__ __forceinline__ uint32_t pack2(float x, float y);
-template <> __device__ __forceinline__ uint32_t pack2<__half>(float x, float y) {
-    __half2 h = __floats2half2_rn(x, y);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float x, float y) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
 
 // A staged operand block is bs rows of bs 16-bit elements, split into column
 // panels of 64 elements (128 B): panel h lives at h * bs * 128 bytes, row r of
@@ -468,70 +361,6 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 }
 
 // ---- host side -------------------------------------------------------------
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    });
-    return fn;
-}
-
-// 2-D view (n_blocks * bs rows, bs columns) of a compressed tensor, boxes of
-// bs rows x 64 columns, 128-byte swizzle.
-int make_block_map(CUtensorMap* map, const void* base, int64_t n_blocks, int bs, int dtype) {
-    EncodeTiledFn fn = get_encode_fn();
-    if (!fn) {
-        set_cuda_error(cudaErrorNotSupported, "cuTensorMapEncodeTiled entry point");
-        return BSP_ERR_CUDA;
-    }
-    cuuint64_t dims[2] = {(cuuint64_t)bs, (cuuint64_t)(n_blocks * bs)};
-    cuuint64_t strides[1] = {(cuuint64_t)bs * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)bs};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, dtype == BSP_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                    2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
-        return BSP_ERR_CUDA;
-    }
-    return BSP_OK;
-}
-
-uint32_t make_idesc(int dtype, int bs, int op) {
-    const uint32_t fmt = dtype == BSP_F16 ? 0u : 1u;
-    const uint32_t a_mn = op == BSP_OP_TN ? 1u : 0u;
-    const uint32_t b_mn = op != BSP_OP_NT ? 1u : 0u;
-    return (1u << 4)                       // fp32 accumulator
-           | (fmt << 7) | (fmt << 10)      // A and B element format
-           | (a_mn << 15) | (b_mn << 16)   // major-ness
-           | ((uint32_t)(bs >> 3) << 17)   // N
-           | ((uint32_t)(bs >> 4) << 24);  // M
-}
-
-int num_sms() {
-    static int cached[64] = {0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
-    if (cached[dev] == 0) {
-        int n = 0;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-        cached[dev] = n;
-    }
-    return cached[dev];
-}
 
 template <typename T, int BS, int OP>
 int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_t n_b, void* out,

@@ -14,7 +14,7 @@ import torch
 from torch import Tensor
 
 from .. import _cabi
-from ..plan import PairPlan, build_pair_plan, run_pair_plan
+from ..plan import Product
 from ..utils.blksprs_tensor import BlksprsTensor
 from ..utils.tools import build_layout_indices, build_packed_indices, cast_for_autocast, count_active_blocks, \
     finalize_layout_cache, prepare_layout_cache
@@ -36,9 +36,9 @@ class _MatmulPlans:
         self.layouts = (sl_x, sl_y, sl_o)
         self.n_x: int | None = None
         self.n_y: int | None = None
-        self.forward: PairPlan | None = None
-        self.grad_x: PairPlan | None = None
-        self.grad_y: PairPlan | None = None
+        self.forward: Product | None = None
+        self.grad_x: Product | None = None
+        self.grad_y: Product | None = None
         self.packed_o: Tensor | None = None
 
     def dims(self):
@@ -75,7 +75,7 @@ def matmul_build_layout_cache(layout_cache: dict | None, sparsity_layout_x: Tens
         plans.forward = plans.grad_x = plans.grad_y = None  # same layouts, other block size class
     if plans.forward is None:
         R, K, C = plans.dims()
-        plans.forward = build_pair_plan(_cabi.OP_NN, layout_cache["layout_indices_o"],
+        plans.forward = Product(_cabi.OP_NN, layout_cache["layout_indices_o"],
                                         layout_cache["packed_indices_x"], layout_cache["packed_indices_y"],
                                         R, K, C, chunks)
 
@@ -96,10 +96,10 @@ def _backward_plans(plans: _MatmulPlans, packed_x: Tensor, packed_y: Tensor, n_x
     chunks = plans.forward.n_chunks
     if plans.grad_x is None:
         lut_x = build_layout_indices(sl_x, n_x)
-        plans.grad_x = build_pair_plan(_cabi.OP_NT, lut_x, plans.packed_o, packed_y, R, K, C, chunks)
+        plans.grad_x = Product(_cabi.OP_NT, lut_x, plans.packed_o, packed_y, R, K, C, chunks)
     if plans.grad_y is None:
         lut_y = build_layout_indices(sl_y, n_y)
-        plans.grad_y = build_pair_plan(_cabi.OP_TN, lut_y, packed_x, plans.packed_o, R, K, C, chunks)
+        plans.grad_y = Product(_cabi.OP_TN, lut_y, packed_x, plans.packed_o, R, K, C, chunks)
 
 
 class _BlockSparseMatmul(torch.autograd.Function):
@@ -110,7 +110,7 @@ class _BlockSparseMatmul(torch.autograd.Function):
         ctx.save_for_backward(x, y, packed_x, packed_y)
         ctx.plans = plans
         ctx.sparsity_block_size = bs
-        return run_pair_plan(plans.forward, x, y, bs)
+        return plans.forward.run(x, y, bs)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
@@ -123,8 +123,8 @@ class _BlockSparseMatmul(torch.autograd.Function):
             grad_output = grad_output.to(x.dtype)
         need_x, need_y = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         _backward_plans(plans, packed_x, packed_y, x.size(0), y.size(0))
-        grad_x = run_pair_plan(plans.grad_x, grad_output, y, bs) if need_x else None
-        grad_y = run_pair_plan(plans.grad_y, x, grad_output, bs) if need_y else None
+        grad_x = plans.grad_x.run(grad_output, y, bs) if need_x else None
+        grad_y = plans.grad_y.run(x, grad_output, bs) if need_y else None
         return grad_x, grad_y, None, None, None, None
 
 

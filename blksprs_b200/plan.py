@@ -112,14 +112,23 @@ def check_device_status(device: torch.device | None = None) -> None:
         raise _cabi.NativeError(code, "device status word")
 
 
-_KERNEL_NAMES = {"auto": _cabi.KERNEL_AUTO, "mma": _cabi.KERNEL_MMA, "umma": _cabi.KERNEL_UMMA}
+_KERNEL_NAMES = {"auto": _cabi.KERNEL_AUTO, "mma": _cabi.KERNEL_MMA, "umma": _cabi.KERNEL_UMMA, "panel": 3}
 _kernel_choice = _KERNEL_NAMES[os.environ.get("BLKSPRS_B200_KERNEL", "auto")]
+KERNEL_PANEL = 3
+
+# "auto" uses the wide-N kernel for block size 64 when panels merge enough work: steps / pairs at
+# or below this ratio (0.5 = every step serves two (A, B) pairs).  Measured on B200: dense-B
+# products (P*V, dO*V^T on an attention layout) gain 1.25-1.35x, random x random layouts (ratio
+# ~0.85) lose, and for block size 128 the per-pair kernel is already at the L2/HBM limits.
+PANEL_STEP_RATIO = float(os.environ.get("BLKSPRS_B200_PANEL_RATIO", "0.58"))
+PANEL_AUTO_BLOCK_SIZES = (64,)
 
 
 def set_kernel(name: str) -> None:
-    """Selects the kernel family for later launches: ``"auto"`` (tcgen05 where it applies, else
-    mma.sync), ``"mma"`` or ``"umma"``.  Meant for tests and profiling; both families are sm_100a
-    CUDA kernels of the same library."""
+    """Selects the kernel family for later launches: ``"auto"`` (the wide-N tcgen05 kernel where
+    panels pay off, the per-pair tcgen05 kernel for other 16-bit block-64/128 products, mma.sync
+    otherwise), ``"mma"``, ``"umma"`` (per-pair tcgen05) or ``"panel"`` (wide-N tcgen05 wherever it
+    applies).  Meant for tests and profiling; all families are sm_100a CUDA kernels of one library."""
     global _kernel_choice
     _kernel_choice = _KERNEL_NAMES[name]
 
@@ -139,3 +148,118 @@ def run_pair_plan(plan: PairPlan, a: Tensor, b: Tensor, bs: int, kernel: int | N
             bs, _cabi.DATA_DTYPE_CODES[a.dtype], plan.op, kernel, _cabi.ptr(status_word(device)),
             _cabi.stream_handle(device)), "bsp_matmul")
     return out
+
+
+@dataclass
+class PanelPlan:
+    op: int
+    n_out: int
+    n_panels: int
+    n_steps: int
+    width: int
+    panel_first: Tensor
+    step_offsets: Tensor
+    steps: Tensor
+    touched: Tensor
+    chunk_begin: Tensor
+    n_chunks: int
+
+
+def build_panel_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor, R: int, K: int, C: int,
+                     width: int, n_chunks: int) -> PanelPlan:
+    """Groups the output blocks of every output row into panels of ``width`` and lists each panel's steps."""
+    device = lut_out.device
+    n_out = lut_out.size(0)
+    (a_sb, a_sr, a_st), (b_sb, b_st, b_sc), T = _walk_strides(op, R, K, C)
+    lib = _cabi.lib()
+    with torch.cuda.device(device):
+        stream = _cabi.stream_handle(device)
+        # panel boundaries: position of every output block inside its (batch, row) run, modulo width
+        idx = torch.arange(n_out, device=device)
+        new_row = torch.ones(n_out, dtype=torch.bool, device=device)
+        if n_out > 1:
+            new_row[1:] = (lut_out[1:, 0] != lut_out[:-1, 0]) | (lut_out[1:, 1] != lut_out[:-1, 1])
+        row_first = torch.cummax(torch.where(new_row, idx, torch.zeros_like(idx)), 0).values
+        starts = torch.nonzero((idx - row_first) % width == 0).flatten()
+        n_panels = starts.numel()
+        panel_first = torch.empty(n_panels + 1, dtype=torch.int32, device=device)
+        panel_first[:n_panels] = starts
+        panel_first[n_panels] = n_out
+        counts = torch.empty(max(n_panels, 1), dtype=torch.int32, device=device)
+        touched = torch.empty(max(n_panels, 1), dtype=torch.int32, device=device)
+        offsets = torch.empty(n_panels + 1, dtype=torch.int32, device=device)
+        total = torch.empty(1, dtype=torch.int64, device=device)
+        ws_bytes = lib.bsp_plan_workspace_bytes(n_panels)
+        ws = torch.empty(ws_bytes // 8, dtype=torch.int64, device=device)
+        walk = (_cabi.ptr(lut_out), _cabi.ptr(panel_first), n_panels, _cabi.ptr(packed_a), a_sb, a_sr, a_st,
+                _cabi.ptr(packed_b), b_sb, b_st, b_sc, T)
+        _cabi.check(lib.bsp_panel_count(*walk, _cabi.ptr(counts), _cabi.ptr(touched), stream), "bsp_panel_count")
+        _cabi.check(lib.bsp_plan_offsets(_cabi.ptr(counts), n_panels, _cabi.ptr(offsets), _cabi.ptr(total),
+                                         _cabi.ptr(ws), ws_bytes, stream), "bsp_plan_offsets")
+        n_steps = int(total.item())
+        if n_steps > 2_147_483_647 // 8:
+            raise ValueError("blksprs_b200: panel plan too large")
+        steps = torch.empty((max(n_steps, 1), 8), dtype=torch.int32, device=device)
+        _cabi.check(lib.bsp_panel_fill(*walk, _cabi.ptr(offsets), _cabi.ptr(steps), stream), "bsp_panel_fill")
+        chunk_begin = torch.empty(n_chunks + 1, dtype=torch.int32, device=device)
+        _cabi.check(lib.bsp_plan_schedule(_cabi.ptr(offsets), n_panels, BLOCK_COST * width, n_chunks,
+                                          _cabi.ptr(chunk_begin), stream), "bsp_plan_schedule")
+    return PanelPlan(op, n_out, n_panels, n_steps, width, panel_first, offsets, steps, touched, chunk_begin, n_chunks)
+
+
+def run_panel_plan(plan: PanelPlan, a: Tensor, b: Tensor, bs: int) -> Tensor:
+    device = a.device
+    out = torch.empty((plan.n_out, bs, bs), dtype=a.dtype, device=device)
+    if plan.n_out == 0:
+        return out
+    with torch.cuda.device(device):
+        _cabi.check(_cabi.lib().bsp_matmul_panel(
+            _cabi.ptr(a), a.size(0), _cabi.ptr(b), b.size(0), _cabi.ptr(out), plan.n_out,
+            _cabi.ptr(plan.panel_first), plan.n_panels, _cabi.ptr(plan.step_offsets), _cabi.ptr(plan.steps),
+            _cabi.ptr(plan.touched), _cabi.ptr(plan.chunk_begin), plan.n_chunks, bs,
+            _cabi.DATA_DTYPE_CODES[a.dtype], plan.op, _cabi.ptr(status_word(device)),
+            _cabi.stream_handle(device)), "bsp_matmul_panel")
+    return out
+
+
+class Product:
+    """One block-sparse product (forward, dX or dY) of a layout triple: its pair plan, and, built on
+    first use for 16-bit data with block size 64 / 128, its panel plan."""
+
+    def __init__(self, op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor, R: int, K: int, C: int,
+                 n_chunks: int):
+        self.op, self.dims = op, (R, K, C)
+        self.lut_out, self.packed_a, self.packed_b = lut_out, packed_a, packed_b
+        self.pair = build_pair_plan(op, lut_out, packed_a, packed_b, R, K, C, n_chunks)
+        self._panels: dict[int, PanelPlan | None] = {}
+
+    @property
+    def n_chunks(self) -> int:
+        return self.pair.n_chunks
+
+    def panel(self, bs: int, dtype: torch.dtype) -> PanelPlan | None:
+        """The panel plan for this block size, or ``None`` where the wide-N kernel does not apply."""
+        if bs not in self._panels:
+            lib = _cabi.lib()
+            code = _cabi.DATA_DTYPE_CODES[dtype]
+            width = lib.bsp_panel_width(code, bs)
+            plan = None
+            if width > 1 and self.pair.n_out > 0 and self.pair.n_pairs > 0:
+                plan = build_panel_plan(self.op, self.lut_out, self.packed_a, self.packed_b, *self.dims, width,
+                                        lib.bsp_matmul_panel_num_chunks(code, bs))
+            self._panels[bs] = plan
+        return self._panels[bs]
+
+    def run(self, a: Tensor, b: Tensor, bs: int) -> Tensor:
+        kernel = _kernel_choice
+        if a.dtype in (torch.float16, torch.bfloat16) and a.size(0) > 0 and b.size(0) > 0 \
+                and ((kernel == KERNEL_PANEL and bs in (64, 128))
+                     or (kernel == _cabi.KERNEL_AUTO and bs in PANEL_AUTO_BLOCK_SIZES)):
+            panel = self.panel(bs, a.dtype)
+            if panel is not None and (kernel == KERNEL_PANEL
+                                      or (bs in PANEL_AUTO_BLOCK_SIZES
+                                          and panel.n_steps <= PANEL_STEP_RATIO * self.pair.n_pairs)):
+                return run_panel_plan(panel, a, b, bs)
+        if kernel == KERNEL_PANEL or a.size(0) == 0 or b.size(0) == 0:
+            kernel = _cabi.KERNEL_AUTO  # without operand blocks only zero blocks are written
+        return run_pair_plan(self.pair, a, b, bs, kernel)

@@ -228,6 +228,49 @@ int bsp_matmul(const void* a, int64_t n_a, const void* b, int64_t n_b,
                int bs, int dtype, int op, int kernel,
                int32_t* status_word, void* stream);
 
+/* ---- wide-N ("panel") variant of the tcgen05 kernel ----------------------
+ * A panel is a run of up to bsp_panel_width() output blocks, consecutive in the
+ * output LUT and in the same (batch, row) of the output layout.  The reference
+ * kernel (blksprs/ops/matmul.py:148-253) re-loads the x tile for every output
+ * tile of a row; here one staged A block serves the whole panel and the panel's
+ * B blocks are multiplied by one wide MMA.  Same results as bsp_matmul. */
+
+/* Output blocks per panel for this (dtype, bs); 0 if the kernel does not apply. */
+int bsp_panel_width(int dtype, int bs);
+
+/* Number of persistent CTAs (= schedule chunks, counted in panels). */
+int bsp_matmul_panel_num_chunks(int dtype, int bs);
+
+/* counts_out[p] (int32) = number of steps of panel p (inner indices t whose A
+ * block exists and that hit at least one B block of the panel); touched_out[p]
+ * (int32) = bit mask of the panel columns hit by any step.  panel_first is
+ * int32 (n_panels+1): first output block of each panel.  Strides as in
+ * bsp_plan_count. */
+int bsp_panel_count(const int64_t* lut_out, const int32_t* panel_first, int64_t n_panels,
+                    const int64_t* packed_a, int64_t a_sb, int64_t a_sr, int64_t a_st,
+                    const int64_t* packed_b, int64_t b_sb, int64_t b_st, int64_t b_sc,
+                    int64_t T, int32_t* counts_out, int32_t* touched_out, void* stream);
+
+/* steps_out (int32, (total_steps, 8)): [0] a_block, [1..4] b_block per panel
+ * column or -1, [5] control word (bits 0-3 present columns, bits 4-7 columns
+ * touched for the first time, bit 8 last step of the panel, bits 12-14 panel
+ * size), [6..7] zero.  step_offsets = exclusive prefix sum of the counts
+ * (bsp_plan_offsets). */
+int bsp_panel_fill(const int64_t* lut_out, const int32_t* panel_first, int64_t n_panels,
+                   const int64_t* packed_a, int64_t a_sb, int64_t a_sr, int64_t a_st,
+                   const int64_t* packed_b, int64_t b_sb, int64_t b_st, int64_t b_sc,
+                   int64_t T, const int32_t* step_offsets, int32_t* steps_out, void* stream);
+
+/* Block-sparse product on a panel plan (fp16 / bf16, bs 64 / 128).  chunk_begin
+ * (int32, n_chunks+1) splits the panels among the persistent CTAs
+ * (bsp_plan_schedule on step_offsets). */
+int bsp_matmul_panel(const void* a, int64_t n_a, const void* b, int64_t n_b,
+                     void* out, int64_t n_out,
+                     const int32_t* panel_first, int64_t n_panels,
+                     const int32_t* step_offsets, const int32_t* steps, const int32_t* touched,
+                     const int32_t* chunk_begin, int32_t n_chunks,
+                     int bs, int dtype, int op, int32_t* status_word, void* stream);
+
 /* Compressed transpose.  Replaces transpose_forward + flow_pull_kernel,
  * blksprs/ops/transpose.py:45-51, blksprs/ops/flow.py:64-111:
  *   out[p] = x[src_index[p]]^T  for p in [0, n_out), where src_index (int64,

@@ -110,7 +110,8 @@ def test_pair_plan_matches_oracle():
         (plans.grad_x, oracle.layout_indices(lx), lambda b, i, k, t: po[b, i, t], lambda b, i, k, t: py[b, k, t], 5),
         (plans.grad_y, oracle.layout_indices(ly), lambda b, k, j, t: px[b, t, k], lambda b, k, j, t: po[b, t, j], 7),
     ]
-    for plan, lut, fa, fb, T in checks:
+    for product, lut, fa, fb, T in checks:
+        plan = product.pair
         offs, pairs = expect(lut, fa, fb, T)
         assert np.array_equal(plan.offsets.cpu().numpy(), offs)
         assert plan.n_pairs == len(pairs)
