@@ -360,7 +360,7 @@ def run_gpu_arm(args):
         x, y, g = workload_values(args.config, lx, ly, lo, bsz, dtype, seed=s + 10 * rank, device=dev)
         sets.append((x, y, g))
 
-    cache = matmul_build_layout_cache({}, lxd, lyd, lod, bsz)
+    cache = matmul_build_layout_cache({}, lxd, lyd, lod)
     plans = cache[_PLANS]
     _backward_plans(plans, cache["packed_indices_x"], cache["packed_indices_y"], sets[0][0].size(0),
                     sets[0][1].size(0))

@@ -17,7 +17,6 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libblksprs_b200.so"
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_RANGE, ERR_DEVICE_TIMEOUT, ERR_TOO_LARGE = range(8)
 # matmul ops / kernel selectors / layout modes
 OP_NN, OP_NT, OP_TN = 0, 1, 2
-KERNEL_AUTO, KERNEL_MMA, KERNEL_UMMA = 0, 1, 2
 LAYOUT_EXACT, LAYOUT_FAST, LAYOUT_OUTER = 0, 1, 2
 
 LAYOUT_DTYPE_CODES = {
@@ -47,18 +46,17 @@ SIGNATURES = {
     "bsp_plan_fill": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64,
                               c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "bsp_plan_schedule": (c_int, [c_void_p, c_int64, c_int32, c_int32, c_void_p, c_void_p]),
-    "bsp_matmul_num_chunks": (c_int, [c_int, c_int, c_int]),
-    "bsp_matmul": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
-                           c_int32, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
-    "bsp_panel_width": (c_int, [c_int, c_int]),
-    "bsp_matmul_panel_num_chunks": (c_int, [c_int, c_int]),
+    "bsp_matmul_mma": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p,
+                               c_int, c_int, c_int, c_void_p, c_void_p]),
+    "bsp_umma_max_width": (c_int, [c_int, c_int]),
+    "bsp_umma_num_ctas": (c_int, [c_int, c_int, c_int]),
     "bsp_panel_count": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
                                 c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "bsp_panel_fill": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
                                c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
-    "bsp_matmul_panel": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
-                                 c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int, c_int, c_int, c_void_p,
-                                 c_void_p]),
+    "bsp_matmul_umma": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int, c_int, c_int, c_int,
+                                c_void_p, c_void_p]),
     "bsp_transpose_blocks": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),
 }
 

@@ -37,15 +37,9 @@ extern "C" const char* bsp_status_string(int status) {
 
 extern "C" const char* bsp_last_cuda_error(void) { return g_cuda_error; }
 
-extern "C" int bsp_matmul_num_chunks(int dtype, int bs, int kernel) {
-    if (kernel == BSP_KERNEL_MMA) return 0;
-    return umma_num_chunks(dtype, bs);
-}
-
-extern "C" int bsp_matmul(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
-                          int64_t n_out, const int32_t* offsets, const int32_t* pairs,
-                          const int32_t* chunk_begin, int32_t n_chunks, int bs, int dtype, int op,
-                          int kernel, int32_t* status_word, void* stream_) {
+extern "C" int bsp_matmul_mma(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
+                              int64_t n_out, const int32_t* offsets, const int32_t* pairs, int bs, int dtype,
+                              int op, int32_t* status_word, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     if (n_a < 0 || n_b < 0 || n_out < 0) return BSP_ERR_INVALID_ARG;
     if (bs < 16 || (bs & (bs - 1))) return BSP_ERR_INVALID_ARG;
@@ -54,24 +48,5 @@ extern "C" int bsp_matmul(const void* a, int64_t n_a, const void* b, int64_t n_b
     if (n_out == 0) return BSP_OK;  // an empty grid is legal (empty output layout)
     if (!out || !offsets) return BSP_ERR_INVALID_ARG;
     if ((n_a > 0 && !a) || (n_b > 0 && !b)) return BSP_ERR_INVALID_ARG;
-
-    bool use_umma;
-    switch (kernel) {
-        case BSP_KERNEL_MMA: use_umma = false; break;
-        case BSP_KERNEL_UMMA:
-            if (!umma_applicable(dtype, bs) || n_a == 0 || n_b == 0) return BSP_ERR_UNSUPPORTED;
-            use_umma = true;
-            break;
-        case BSP_KERNEL_AUTO:
-            // without operand blocks there is nothing to stage: the mma.sync
-            // kernel then only writes the zero blocks
-            use_umma = umma_applicable(dtype, bs) && n_a > 0 && n_b > 0 && chunk_begin && n_chunks > 0;
-            break;
-        default: return BSP_ERR_INVALID_ARG;
-    }
-    if (use_umma)
-        return launch_matmul_umma(a, n_a, b, n_b, out, n_out, offsets, pairs, chunk_begin, n_chunks, bs,
-                                  dtype, op, status_word, stream);
-    return launch_matmul_mma(a, n_a, b, n_b, out, n_out, offsets, pairs, bs, dtype, op, status_word,
-                             stream);
+    return launch_matmul_mma(a, n_a, b, n_b, out, n_out, offsets, pairs, bs, dtype, op, status_word, stream);
 }

@@ -76,10 +76,5 @@ int launch_matmul_mma(const void* a, int64_t n_a, const void* b, int64_t n_b, vo
                       int64_t n_out, const int32_t* offsets, const int32_t* pairs, int bs,
                       int dtype, int op, int32_t* status_word, cudaStream_t stream);
 bool umma_applicable(int dtype, int bs);
-int umma_num_chunks(int dtype, int bs);
-int launch_matmul_umma(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
-                       int64_t n_out, const int32_t* offsets, const int32_t* pairs,
-                       const int32_t* chunk_begin, int32_t n_chunks, int bs, int dtype,
-                       int op, int32_t* status_word, cudaStream_t stream);
 
 }  // namespace bsp

@@ -1,31 +1,32 @@
-// Block-sparse matmul on a pair plan with 5th-generation tensor cores
-// (tcgen05.mma, accumulators in tensor memory) for 16-bit data and block sizes
-// 64 and 128.
+// Block-sparse matmul on 5th-generation tensor cores (tcgen05.mma, accumulators in tensor
+// memory) for fp16 / bf16 data and block sizes 64 and 128.
 //
-// One persistent CTA per SM walks a contiguous range of output blocks
-// (bsp_plan_schedule).  Roles, by warp:
-//   warp 0      producer: streams the range's (a_block, b_block) pairs, and for
-//               each pair TMA-loads the two bs x bs operand blocks (128-byte
-//               swizzle, global orientation) into the next free ring stage
-//   warp 1      MMA issuer: one thread issues bs/16 tcgen05.mma per pair into
-//               the current accumulator, releases the stage with
-//               tcgen05.commit, and hands a finished accumulator to the
-//               epilogue
-//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator, convert to the
-//               output type, write the output block; blocks without pairs are
-//               written as zeros without touching tensor memory
-// The transposed products of the backward pass (BSP_OP_NT, BSP_OP_TN) use the
-// same staged blocks; only the major-ness bits of the shared-memory matrix
-// descriptors and of the instruction descriptor change.
+// The work list is a step plan (plan_panel.cu): the output blocks of one output row are grouped
+// into panels of G (1 or 2) blocks; a step is one inner index t whose A block exists and that
+// hits at least one B block of the panel.  Per step one A block and the step's B blocks are
+// staged; the B blocks of neighbouring panel columns lie side by side in shared memory, so a run
+// of present columns is multiplied by ONE tcgen05.mma of N = run x bs, and the A block is fetched
+// once per step instead of once per (A, B) pair.  With G = 1 a step is a single (A, B) pair.
 //
-// Every wait is bounded (about one second); a wait that runs out records
-// BSP_ERR_DEVICE_TIMEOUT in the status word, all roles leave their loops,
-// outstanding copies and MMAs are drained with bounded waits, tensor memory is
-// freed and the kernel returns.
-#include <cuda.h>
-
-#include <mutex>
-
+// A ring entry is one (step, k-chunk): 64 of the bs contraction indices of the step's blocks,
+// so that for bs = 128 the MMAs of the first half can start while the second half is in flight.
+// A block read K-major contributes its 64-column half k (bs rows x 128 B); a block read
+// MN-major contributes rows [64k, 64k+64) as bs/64 sub-tiles of 64 rows x 128 B.  The
+// transposed products of the backward pass (BSP_OP_NT, BSP_OP_TN) use the same staged data;
+// only the major-ness bits of the shared-memory and instruction descriptors change.
+//
+// Persistent CTAs (1 to 3 per SM), roles by warp:
+//   warp 0      producer: lane l owns ring stage l, polls that stage's "empty" barrier and
+//               issues the TMA copies of its entry (128-byte swizzle) as soon as it is free
+//   warp 1      MMA issuer: one thread issues four tcgen05.mma (K = 16 each) per run and entry,
+//               releases the stage with tcgen05.commit, and hands a finished accumulator group
+//               (the G accumulators of a panel, adjacent tensor-memory columns) to the epilogue
+//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulators, convert, write the output blocks
+//               with 32-byte stores; blocks no step touched are written as zeros
+//
+// Every wait is bounded (about one second): a wait that runs out records
+// BSP_ERR_DEVICE_TIMEOUT in the status word, all roles leave their loops, outstanding copies
+// and MMAs are drained with bounded waits, tensor memory is freed and the kernel returns.
 #include "common.cuh"
 #include "umma_common.cuh"
 
@@ -36,9 +37,7 @@ using namespace umma;
 namespace {
 
 constexpr int kThreads = 192;
-constexpr uint32_t kFlagLast = 1u;  // stage holds the last pair of its output block
-constexpr int kPairLastBit = 0x40000000;   // set on pairs[2p] when p is the last pair of its block
-constexpr int kPairIndexMask = 0x3fffffff;
+constexpr uint32_t kCtrlLast = 0x100u;
 
 #ifdef BSP_UMMA_PROFILE
 // Debug build only: per-CTA cycle counters (8 per CTA) read back by bsp_debug_read_prof.
@@ -54,71 +53,59 @@ __device__ long long g_prof[1024 * 8];
 #define PROF_STORE(i, v)
 #endif
 
-template <int BS> struct Cfg;
-#ifndef BSP_UMMA64_STAGES
-#define BSP_UMMA64_STAGES 4
-#endif
-#ifndef BSP_UMMA64_CTAS
-#define BSP_UMMA64_CTAS 3
-#endif
-#ifndef BSP_UMMA64_ACCS
-#define BSP_UMMA64_ACCS 2
-#endif
-
-template <> struct Cfg<64> {
-    static constexpr int kStages = BSP_UMMA64_STAGES;  // x 16 KiB
-    static constexpr int kAccs = BSP_UMMA64_ACCS;      // x 64 columns
-    static constexpr int kTmemCols = 64 * BSP_UMMA64_ACCS;
-    static constexpr int kCtasPerSm = BSP_UMMA64_CTAS;
+// Per (block size, panel width): ring depth, accumulator groups (of G x bs tensor-memory
+// columns each) and resident CTAs per SM.  Shared memory: stages x (1 + G) x bs x 128 bytes.
+template <int BS, int G> struct PCfg;
+template <> struct PCfg<64, 1> {   // 3 x (4 x 16 KiB), 3 x 128 columns
+    static constexpr int kStages = 4, kGroups = 2, kCtasPerSm = 3;
 };
-template <> struct Cfg<128> {
-    static constexpr int kStages = 3;     // 3 x 64 KiB
-    static constexpr int kAccs = 4;       // 4 x 128 columns
-    static constexpr int kTmemCols = 512;
-    static constexpr int kCtasPerSm = 1;
+template <> struct PCfg<64, 2> {   // 2 x (4 x 24 KiB), 2 x 256 columns
+    static constexpr int kStages = 4, kGroups = 2, kCtasPerSm = 2;
+};
+template <> struct PCfg<128, 1> {  // 6 x 32 KiB, 4 x 128 columns
+    static constexpr int kStages = 6, kGroups = 4, kCtasPerSm = 1;
+};
+template <> struct PCfg<128, 2> {  // 4 x 48 KiB, 2 x 256 columns
+    static constexpr int kStages = 4, kGroups = 2, kCtasPerSm = 1;
 };
 
-template <int BS>
-struct SmemLayout {
-    static constexpr int kBlockBytes = BS * BS * 2;
-    static constexpr int kStageBytes = 2 * kBlockBytes;
-    static constexpr int kDataBytes = Cfg<BS>::kStages * kStageBytes;
-    // after the data: full[S], empty[S], tmem_full[A], tmem_empty[A], drain (8 B each),
-    // flags[S] (4 B), armed[S] (4 B), tmem base (4 B), abort flag (4 B)
-    static constexpr int kBarBytes = (2 * Cfg<BS>::kStages + 2 * Cfg<BS>::kAccs + 1) * 8;
-    static constexpr int kMiscBytes = (2 * Cfg<BS>::kStages + 2) * 4;
-    static constexpr int kTotal = kDataBytes + kBarBytes + kMiscBytes + 1024 /* alignment slack */;
+constexpr int tmem_cols_pow2(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
+
+template <int BS, int G>
+struct PSmem {
+    static constexpr int kChunkBytes = BS * 128;           // one block's share of a ring entry: bs x 64 elements
+    static constexpr int kStageBytes = (1 + G) * kChunkBytes;
+    static constexpr int kDataBytes = PCfg<BS, G>::kStages * kStageBytes;
+    static constexpr int kBarBytes = (2 * PCfg<BS, G>::kStages + 2 * PCfg<BS, G>::kGroups + 1) * 8;
+    static constexpr int kMiscBytes = (2 * PCfg<BS, G>::kStages + 2) * 4;
+    static constexpr int kTotal = kDataBytes + kBarBytes + kMiscBytes + 1024;
 };
 
-// A staged operand block is bs rows of bs 16-bit elements, split into column
-// panels of 64 elements (128 B): panel h lives at h * bs * 128 bytes, row r of
-// a panel at r * 128, 16-byte chunks XOR-swizzled by (r % 8).
-//
-// Read K-major (the contraction index runs along the rows' 64-element panels):
-//   8-row groups are 1024 B apart (SBO); k-step s (16 elements) starts
-//   (s / 4) panels in, (s % 4) * 32 bytes into the 128-byte row.
-// Read MN-major (the contraction index runs down the rows):
-//   the 64-wide panels are the M/N atoms, bs * 128 bytes apart (LBO); 8-row
-//   k-groups are 1024 B apart (SBO); k-step s starts 16 rows = 2048 B further.
+// Shared-memory matrix descriptors of a ring entry (all 128-byte swizzle, 8-row groups 1024 B
+// apart).  K-major: rows are M/N indices, 16 contraction elements = 32 bytes along the row.
+// MN-major: rows are contraction indices (16 rows = 2048 B per MMA), the M/N extent is cut
+// into 64-wide atoms of 64 rows x 128 B = 8 KiB, `LBO` apart.
 template <int BS, bool MN_MAJOR>
-__device__ __forceinline__ uint64_t operand_desc(uint32_t base, int kstep) {
-    if (MN_MAJOR) return make_smem_desc(base + kstep * 2048, BS * 128, 1024);
-    return make_smem_desc(base + (kstep >> 2) * (BS * 128) + (kstep & 3) * 32, 16, 1024);
+__device__ __forceinline__ uint64_t chunk_desc(uint32_t base, int kk) {
+    if (MN_MAJOR) return make_smem_desc(base + kk * 2048, 8192, 1024);
+    return make_smem_desc(base + kk * 32, 16, 1024);
 }
 
-template <typename T, int BS, int OP>
-__global__ void __launch_bounds__(kThreads, Cfg<BS>::kCtasPerSm)
+template <typename T, int BS, int OP, int G>
+__global__ void __launch_bounds__(kThreads, PCfg<BS, G>::kCtasPerSm)
 matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    int64_t n_a, int64_t n_b, T* __restrict__ out,
-                   const int32_t* __restrict__ offsets, const int32_t* __restrict__ pairs,
-                   const int32_t* __restrict__ chunk_begin, uint32_t idesc,
-                   int32_t* __restrict__ status_word) {
-    using C = Cfg<BS>;
-    using L = SmemLayout<BS>;
-    constexpr int S = C::kStages, A = C::kAccs;
-    constexpr bool A_MN = (OP == BSP_OP_TN);   // A block is read transposed
-    constexpr bool B_MN = (OP != BSP_OP_NT);   // B block rows are the contraction index
-    constexpr int KSTEPS = BS / 16;
+                   const int32_t* __restrict__ panel_first, const int32_t* __restrict__ step_off,
+                   const int32_t* __restrict__ steps, const int32_t* __restrict__ touched,
+                   const int32_t* __restrict__ unit_panel, const int32_t* __restrict__ unit_step,
+                   int n_units, uint32_t idesc_no_n, int32_t* __restrict__ status_word) {
+    using C = PCfg<BS, G>;
+    using L = PSmem<BS, G>;
+    constexpr int S = C::kStages, NG = C::kGroups, H = BS / 64, KC = BS / 64;
+    constexpr bool A_MN = (OP == BSP_OP_TN);
+    constexpr bool B_MN = (OP != BSP_OP_NT);
+    constexpr int TMEM_COLS = tmem_cols_pow2(NG * G * BS);
+    static_assert(S <= 32 && G <= 4 && G * BS <= 256, "panel configuration out of range");
 
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_addr(smem_raw);
@@ -126,14 +113,13 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     unsigned char* data_ptr = smem_raw + (data - raw);
     const uint32_t bars = data + L::kDataBytes;
     const uint32_t full_bar = bars, empty_bar = bars + 8 * S, tfull_bar = bars + 16 * S,
-                   tempty_bar = tfull_bar + 8 * A, drain_bar = tempty_bar + 8 * A;
-    volatile uint32_t* flags = reinterpret_cast<volatile uint32_t*>(data_ptr + L::kDataBytes + L::kBarBytes);
-    volatile int* armed = reinterpret_cast<volatile int*>(flags + S);
+                   tempty_bar = tfull_bar + 8 * NG, drain_bar = tempty_bar + 8 * NG;
+    volatile uint32_t* ctrl_slot = reinterpret_cast<volatile uint32_t*>(data_ptr + L::kDataBytes + L::kBarBytes);
+    volatile int* armed = reinterpret_cast<volatile int*>(ctrl_slot + S);
     volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(armed + S);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int blk_begin = chunk_begin[blockIdx.x], blk_end = chunk_begin[blockIdx.x + 1];
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
@@ -141,7 +127,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             mbar_init(empty_bar + 8 * s, 1);
             armed[s] = -1;
         }
-        for (int i = 0; i < A; ++i) {
+        for (int i = 0; i < NG; ++i) {
             mbar_init(tfull_bar + 8 * i, 1);
             mbar_init(tempty_bar + 8 * i, 4);
         }
@@ -152,7 +138,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_addr((const void*)tmem_base_slot)), "r"((uint32_t)C::kTmemCols) : "memory");
+                     ::"r"(smem_addr((const void*)tmem_base_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -160,50 +146,100 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
 
-    if (blk_begin < blk_end) {
-        const int pr_begin = offsets[blk_begin], pr_end = offsets[blk_end];
-
+    // Work is dealt in units (contiguous panel ranges of about equal cost): this CTA takes units
+    // blockIdx.x, blockIdx.x + gridDim.x, ...  All CTAs therefore sweep the output in step, so the
+    // operand blocks of one batch are used by all SMs at about the same time and stay in L2.
+    // Inside a unit the i-th ring entry uses stage i % S; a stage's barrier parity is its use count.
+    if ((int)blockIdx.x < n_units) {
         if (warp == 0) {
-            // ---------------- producer ----------------
-            // Pairs are handled in rounds of S: in a round lane l (< S) owns pair p0 + l and ring
-            // stage l.  Each lane polls its own stage's "empty" barrier and issues its two block
-            // copies as soon as that stage is free, so up to S copies are issued per instruction.
-            const int2* pairs2 = reinterpret_cast<const int2*>(pairs);
-            uint32_t phase = 0;
-            auto load_round = [&](int p0) -> int2 {
-                const int i = p0 + lane;
-                return (lane < S && i < pr_end) ? pairs2[i] : make_int2(0, 0);
+            // ---------------- producer: lane l owns ring stage l ----------------
+            // ring entry = (step, k-chunk); absolute entry index = step * KC + k-chunk
+            const int4* recs = reinterpret_cast<const int4*>(steps);
+            auto unit_range = [&](int uu, int& b, int& e) {
+                if (uu < n_units) {
+                    b = unit_step[uu] * KC;
+                    e = unit_step[uu + 1] * KC;
+                } else {
+                    b = e = 0;
+                }
             };
-            int2 cur = load_round(pr_begin);
+            auto load_rec = [&](int pos, int end, int4& r0, int4& r1) {
+                const int e = pos + lane;
+                if (lane < S && e < end) {
+                    const int64_t i = e / KC;
+                    r0 = recs[2 * i];
+                    r1 = recs[2 * i + 1];
+                } else {
+                    r0 = make_int4(0, -1, -1, -1);
+                    r1 = make_int4(-1, 0, 0, 0);
+                }
+            };
+            int u = blockIdx.x, ub, ue, nub, nue;
+            unit_range(u, ub, ue);
+            unit_range(u + gridDim.x, nub, nue);
+            int pos = ub;
+            int4 c0, c1, n0, n1;
+            load_rec(pos, ue, c0, c1);
+            uint32_t uses = 0;  // how often this lane's stage has been filled
             bool alive = true;
             PROF_DECL(w_empty);
             PROF_T0(t_start);
-            for (int p0 = pr_begin; p0 < pr_end && alive; p0 += S) {
-                const int2 nxt = load_round(p0 + S);
-                if (lane < S && p0 + lane < pr_end) {
-                    int ia = cur.x & kPairIndexMask, ib = cur.y;
-                    const uint32_t last = (cur.x & kPairLastBit) ? kFlagLast : 0u;
-                    if (ia >= n_a || ib < 0 || ib >= n_b) {
+            while (u < n_units && alive) {
+                // where the next round starts: further into this unit, or the next unit's head
+                int npos, nend;
+                const bool unit_done = pos + S >= ue;
+                if (!unit_done) { npos = pos + S; nend = ue; } else { npos = nub; nend = nue; }
+                load_rec(npos, nend, n0, n1);
+                if (lane < S && pos + lane < ue) {
+                    const int kc = (pos + lane) % KC;
+                    int ia = c0.x;
+                    int ib[4] = {c0.y, c0.z, c0.w, c1.x};
+                    const uint32_t ctrl = (uint32_t)c1.y;
+                    const uint32_t present = ctrl & 0xFu;
+                    bool bad = ia < 0 || ia >= n_a;
+#pragma unroll
+                    for (int q = 0; q < G; ++q)
+                        if ((present >> q) & 1u) bad |= ib[q] < 0 || ib[q] >= n_b;
+                    if (bad) {
                         if (status_word) *status_word = BSP_ERR_DEVICE_RANGE;
                         ia = 0;
-                        ib = 0;
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) ib[q] = 0;
                     }
-                    const uint32_t ebar = empty_bar + 8 * lane;
-                    const uint32_t fbar = full_bar + 8 * lane;
+                    const uint32_t phase = uses & 1u;
+                    const uint32_t ebar = empty_bar + 8 * lane, fbar = full_bar + 8 * lane;
                     const uint32_t sa = data + lane * L::kStageBytes;
-                    const uint32_t sb = sa + L::kBlockBytes;
-                    PROF_T0(tw);
+                    const uint32_t sb = sa + L::kChunkBytes;
                     unsigned long long t0 = 0;
+                    PROF_T0(tw);
                     for (uint32_t spins = 1;; ++spins) {
                         if (mbar_try_wait(ebar, phase ^ 1u)) {
-                            flags[lane] = last;
+                            PROF_ADD(w_empty, tw);
+                            // first-touch flags count for the step's first chunk only; the panel ends
+                            // with the step's last chunk
+                            ctrl_slot[lane] = (ctrl & (kc == 0 ? ~0u : ~0xF0u)) & (kc == KC - 1 ? ~0u : ~kCtrlLast);
                             armed[lane] = (int)phase;
-                            mbar_arrive_expect_tx(fbar, L::kStageBytes);
+                            mbar_arrive_expect_tx(fbar, (1 + __popc(present)) * L::kChunkBytes);
+                            if (A_MN) {
 #pragma unroll
-                            for (int h = 0; h < BS / 64; ++h) {
-                                tma_load_2d(sa + h * (BS * 128), &map_a, h * 64, ia * BS, fbar);
-                                tma_load_2d(sb + h * (BS * 128), &map_b, h * 64, ib * BS, fbar);
+                                for (int h = 0; h < H; ++h)
+                                    tma_load_2d(sa + h * 8192, &map_a, h * 64, ia * BS + kc * 64, fbar);
+                            } else {
+                                tma_load_2d(sa, &map_a, kc * 64, ia * BS, fbar);
                             }
+#pragma unroll
+                            for (int q = 0; q < G; ++q) {
+                                if ((present >> q) & 1u) {
+                                    if (B_MN) {
+#pragma unroll
+                                        for (int h = 0; h < H; ++h)
+                                            tma_load_2d(sb + (q * H + h) * 8192, &map_b, h * 64, ib[q] * BS + kc * 64, fbar);
+                                    } else {
+                                        tma_load_2d(sb + q * L::kChunkBytes, &map_b, kc * 64, ib[q] * BS, fbar);
+                                    }
+                                }
+                            }
+                            ++uses;
                             break;
                         }
                         if ((spins & 0xff) == 0) {
@@ -216,11 +252,17 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             }
                         }
                     }
-                    PROF_ADD(w_empty, tw);
                 }
                 alive = __all_sync(0xffffffffu, alive);
-                phase ^= 1u;
-                cur = nxt;
+                if (unit_done) {
+                    u += gridDim.x;
+                    ub = nub;
+                    ue = nue;
+                    unit_range(u + gridDim.x, nub, nue);
+                }
+                pos = npos;
+                c0 = n0;
+                c1 = n1;
             }
             if (lane == 0) {
                 PROF_STORE(0, clock64() - t_start);
@@ -228,111 +270,166 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             }
         } else if (warp == 1) {
             // ---------------- MMA issuer ----------------
-            if (lane == 0) {
-                int stage = 0, acc = 0;
-                uint32_t phase = 0, acc_phase = 0;
-                bool first = true;
+            // The whole warp runs this loop converged and one elected lane issues each MMA / commit:
+            // stage, descriptor and accumulator arithmetic is then warp-uniform (uniform registers)
+            // instead of one diverged lane's, which shortens the issue path measurably.
+            {
+                int grp = 0;
+                uint32_t stage_parity = 0;  // bit s = parity of the next fill of stage s
+                uint32_t grp_phase = 0;
+                bool new_panel = true, alive = true;
                 PROF_DECL(w_full);
                 PROF_DECL(w_tempty);
                 PROF_T0(t_start);
-                for (int pr = pr_begin; pr < pr_end; ++pr) {
-                    if (first) {
-                        PROF_T0(tw);
-                        if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, status_word)) break;
-                        PROF_ADD(w_tempty, tw);
-                    }
-                    PROF_T0(tw2);
-                    if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status_word)) break;
-                    PROF_ADD(w_full, tw2);
-                    tc_fence_after();
-                    const uint32_t fl = flags[stage];
-                    const uint32_t sa = data + stage * L::kStageBytes;
-                    const uint32_t sb = sa + L::kBlockBytes;
-                    const uint32_t d_tmem = tmem_base + acc * BS;
+                int u = blockIdx.x;
+                int n_entries = (unit_step[u + 1] - unit_step[u]) * KC;
+                while (u < n_units && alive) {
+                    const int nu = u + gridDim.x;
+                    const int next_entries = nu < n_units ? (unit_step[nu + 1] - unit_step[nu]) * KC : 0;
+                    int stage = 0;
+                    for (int e = 0; e < n_entries; ++e) {
+                        if (new_panel) {
+                            PROF_T0(tw);
+                            if (!mbar_wait(tempty_bar + 8 * grp, grp_phase ^ 1u, abort_flag, status_word)) { alive = false; break; }
+                            PROF_ADD(w_tempty, tw);
+                        }
+                        PROF_T0(tw2);
+                        if (!mbar_wait(full_bar + 8 * stage, (stage_parity >> stage) & 1u, abort_flag, status_word)) { alive = false; break; }
+                        PROF_ADD(w_full, tw2);
+                        stage_parity ^= 1u << stage;
+                        tc_fence_after();
+                        const uint32_t ctrl = ctrl_slot[stage];
+                        const uint32_t present = ctrl & 0xFu, first = (ctrl >> 4) & 0xFu;
+                        const uint32_t sa = data + stage * L::kStageBytes;
+                        const uint32_t sb = sa + L::kChunkBytes;
+                        const uint32_t d0 = tmem_base + grp * (G * BS);
+                        if constexpr (G == 1) {
+                            // a step is one (A, B) pair
+                            const uint32_t idesc = idesc_no_n | ((uint32_t)(BS >> 3) << 17);
 #pragma unroll
-                    for (int k = 0; k < KSTEPS; ++k) {
-                        tc_mma_f16(d_tmem, operand_desc<BS, A_MN>(sa, k), operand_desc<BS, B_MN>(sb, k),
-                                   idesc, (first && k == 0) ? 0u : 1u);
+                            for (int kk = 0; kk < 4; ++kk) {
+                                tc_mma_f16_elect(d0, chunk_desc<BS, A_MN>(sa, kk), chunk_desc<BS, B_MN>(sb, kk), idesc,
+                                           ((first & 1u) && kk == 0) ? 0u : 1u);
+                            }
+                        } else {
+                            // one MMA chain per run of present columns with equal "first" status
+                            int q = 0;
+                            while (q < G) {
+                                if (!((present >> q) & 1u)) { ++q; continue; }
+                                const int q0 = q;
+                                const uint32_t f = (first >> q) & 1u;  // zero on later chunks of a step
+                                ++q;
+                                while (q < G && ((present >> q) & 1u) && ((first >> q) & 1u) == f) ++q;
+                                const uint32_t n = (uint32_t)(q - q0) * BS;
+                                const uint32_t idesc = idesc_no_n | ((n >> 3) << 17);
+                                // the run's first B sub-tile: K-major blocks follow each other row after
+                                // row, MN-major blocks are bs/64 atoms of 8 KiB each
+                                const uint32_t sbq = sb + (B_MN ? q0 * H * 8192 : q0 * L::kChunkBytes);
+#pragma unroll
+                                for (int kk = 0; kk < 4; ++kk) {
+                                    tc_mma_f16_elect(d0 + q0 * BS, chunk_desc<BS, A_MN>(sa, kk),
+                                               chunk_desc<BS, B_MN>(sbq, kk), idesc, (f && kk == 0) ? 0u : 1u);
+                                }
+                            }
+                        }
+                        tc_commit_elect(empty_bar + 8 * stage);
+                        new_panel = false;
+                        if (ctrl & kCtrlLast) {
+                            tc_commit_elect(tfull_bar + 8 * grp);
+                            new_panel = true;
+                            if (++grp == NG) { grp = 0; grp_phase ^= 1u; }
+                        }
+                        if (++stage == S) stage = 0;
                     }
-                    tc_commit(empty_bar + 8 * stage);
-                    first = false;
-                    if (fl & kFlagLast) {
-                        tc_commit(tfull_bar + 8 * acc);
-                        first = true;
-                        if (++acc == A) { acc = 0; acc_phase ^= 1u; }
-                    }
-                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                    u = nu;
+                    n_entries = next_entries;
                 }
-                // make sure no MMA is still running before tensor memory is freed
-                PROF_STORE(2, clock64() - t_start);
-                PROF_STORE(3, w_full);
-                PROF_STORE(4, w_tempty);
-                tc_commit(drain_bar);
+                if (lane == 0) PROF_STORE(2, clock64() - t_start);
+                if (lane == 0) PROF_STORE(3, w_full);
+                if (lane == 0) PROF_STORE(4, w_tempty);
+                tc_commit_elect(drain_bar);
                 mbar_wait(drain_bar, 0, abort_flag, status_word);
             }
         } else {
             // ---------------- epilogue ----------------
-            const int q = warp & 3;  // tensor-memory subpartition of this warp
+            const int wq = warp & 3;  // tensor-memory subpartition of this warp
             constexpr int ROWS_PER_WARP = BS / 4;
             const bool row_valid = lane < ROWS_PER_WARP;
-            const int row = q * ROWS_PER_WARP + lane;
-            int acc = 0;
-            uint32_t acc_phase = 0;
+            const int row = wq * ROWS_PER_WARP + lane;
+            int grp = 0;
+            uint32_t grp_phase = 0;
             bool alive = true;
             PROF_DECL(w_tfull);
             PROF_T0(t_start);
-            for (int w0 = blk_begin; w0 < blk_end && alive; w0 += 32) {
-                const int bi = w0 + lane;
-                const int my_n = bi < blk_end ? offsets[bi + 1] - offsets[bi] : 0;
-                const int m = min(32, blk_end - w0);
-                for (int j = 0; j < m && alive; ++j) {
-                    const int n = __shfl_sync(0xffffffffu, my_n, j);
-                    T* o = out + (int64_t)(w0 + j) * BS * BS;
-                    if (n == 0) {
-                        // this warp zeroes its quarter of the block
-                        uint4* dst = reinterpret_cast<uint4*>(o + (int64_t)q * ROWS_PER_WARP * BS);
-                        constexpr int VECS = ROWS_PER_WARP * BS * 2 / 16;
-                        for (int i = lane; i < VECS; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
-                        continue;
+            auto zero_quarter = [&](T* o) {
+                uint4* dst = reinterpret_cast<uint4*>(o + (int64_t)wq * ROWS_PER_WARP * BS);
+                constexpr int VECS = ROWS_PER_WARP * BS * 2 / 16;
+                for (int i = lane; i < VECS; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
+            };
+            for (int u = blockIdx.x; u < n_units && alive; u += gridDim.x) {
+                const int pn_begin = unit_panel[u], pn_end = unit_panel[u + 1];
+                for (int w0 = pn_begin; w0 < pn_end && alive; w0 += 32) {
+                    const int pi = w0 + lane;
+                    int my_first = 0, my_g = 0, my_steps = 0, my_touched = 0;
+                    if (pi < pn_end) {
+                        my_first = panel_first[pi];
+                        my_g = panel_first[pi + 1] - my_first;
+                        my_steps = step_off[pi + 1] - step_off[pi];
+                        my_touched = touched[pi];
                     }
-                    PROF_T0(tw);
-                    if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, status_word)) {
-                        alive = false;
-                    }
-                    PROF_ADD(w_tfull, tw);
-                    alive = __all_sync(0xffffffffu, alive);
-                    if (!alive) break;
-                    tc_fence_after();
-                    const uint32_t taddr = tmem_base + acc * BS + ((uint32_t)(q * 32) << 16);
+                    const int m = min(32, pn_end - w0);
+                    for (int j = 0; j < m && alive; ++j) {
+                        const int first = __shfl_sync(0xffffffffu, my_first, j);
+                        const int g = __shfl_sync(0xffffffffu, my_g, j);
+                        const int nsteps = __shfl_sync(0xffffffffu, my_steps, j);
+                        const int tmask = __shfl_sync(0xffffffffu, my_touched, j);
+                        if (nsteps == 0) {
+                            for (int q = 0; q < g; ++q) zero_quarter(out + (int64_t)(first + q) * BS * BS);
+                            continue;
+                        }
+                        PROF_T0(tw);
+                        if (!mbar_wait(tfull_bar + 8 * grp, grp_phase, abort_flag, status_word)) alive = false;
+                        PROF_ADD(w_tfull, tw);
+                        alive = __all_sync(0xffffffffu, alive);
+                        if (!alive) break;
+                        tc_fence_after();
+                        for (int q = 0; q < g; ++q) {
+                            T* o = out + (int64_t)(first + q) * BS * BS;
+                            if (!((tmask >> q) & 1)) {
+                                zero_quarter(o);
+                                continue;
+                            }
+                            const uint32_t taddr = tmem_base + grp * (G * BS) + q * BS + ((uint32_t)(wq * 32) << 16);
 #pragma unroll
-                    for (int c0 = 0; c0 < BS; c0 += 32) {
-                        uint32_t v[32];
-                        tc_ld32(taddr + c0, v);
-                        tc_wait_ld();
-                        if (row_valid) {
-                            // 32 columns = 64 bytes of the row: two 32-byte stores, each a whole sector
-                            T* dst = o + (int64_t)row * BS + c0;
+                            for (int c0 = 0; c0 < BS; c0 += 32) {
+                                uint32_t v[32];
+                                tc_ld32(taddr + c0, v);
+                                tc_wait_ld();
+                                if (row_valid) {
+                                    // 32 columns = 64 bytes of the row: two 32-byte stores, each a whole sector
+                                    T* dst = o + (int64_t)row * BS + c0;
 #pragma unroll
-                            for (int i = 0; i < 2; ++i) {
-                                uint32_t u[8];
+                                    for (int i = 0; i < 2; ++i) {
+                                        uint32_t w8[8];
 #pragma unroll
-                                for (int e = 0; e < 8; ++e)
-                                    u[e] = pack2<T>(__uint_as_float(v[16 * i + 2 * e]),
-                                                    __uint_as_float(v[16 * i + 2 * e + 1]));
-                                st_global_32B(dst + 16 * i, u);
+                                        for (int e = 0; e < 8; ++e)
+                                            w8[e] = pack2<T>(__uint_as_float(v[16 * i + 2 * e]),
+                                                             __uint_as_float(v[16 * i + 2 * e + 1]));
+                                        st_global_32B(dst + 16 * i, w8);
+                                    }
+                                }
                             }
                         }
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty_bar + 8 * grp);
+                        if (++grp == NG) { grp = 0; grp_phase ^= 1u; }
                     }
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
-                    if (++acc == A) { acc = 0; acc_phase ^= 1u; }
                 }
             }
             if (warp == 2 && lane == 0) {
                 PROF_STORE(5, clock64() - t_start);
                 PROF_STORE(6, w_tfull);
-                PROF_STORE(7, (long long)(pr_end - pr_begin) * 100000 + (blk_end - blk_begin));
             }
         }
     }
@@ -341,7 +438,6 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     tc_fence_before();
     __syncthreads();
     if (*abort_flag && threadIdx.x == 0) {
-        // bounded wait for copies that were issued but never consumed
         for (int s = 0; s < S; ++s) {
             const int ph = armed[s];
             if (ph >= 0) {
@@ -356,35 +452,52 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
-                     ::"r"(tmem_base), "r"((uint32_t)C::kTmemCols) : "memory");
+                     ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
     }
 }
 
-// ---- host side -------------------------------------------------------------
-
-template <typename T, int BS, int OP>
+template <typename T, int BS, int OP, int G>
 int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_t n_b, void* out,
-               const int32_t* offsets, const int32_t* pairs, const int32_t* chunk_begin,
-               int32_t n_chunks, int dtype, int32_t* status_word, cudaStream_t stream) {
-    auto kern = matmul_umma_kernel<T, BS, OP>;
-    constexpr int smem = SmemLayout<BS>::kTotal;
+               const int32_t* panel_first, const int32_t* step_off, const int32_t* steps,
+               const int32_t* touched, const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units,
+               int dtype, int32_t* status_word, cudaStream_t stream) {
+    auto kern = matmul_umma_kernel<T, BS, OP, G>;
+    constexpr int smem = PSmem<BS, G>::kTotal;
     BSP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<n_chunks, kThreads, smem, stream>>>(ma, mb, n_a, n_b, (T*)out, offsets, pairs, chunk_begin,
-                                               make_idesc(dtype, BS, OP), status_word);
+    const uint32_t idesc_no_n = make_idesc(dtype, BS, OP) & ~(0x3Fu << 17);
+    int ctas = num_sms() * PCfg<BS, G>::kCtasPerSm;
+    if (ctas > n_units) ctas = n_units;
+    kern<<<ctas, kThreads, smem, stream>>>(ma, mb, n_a, n_b, (T*)out, panel_first, step_off, steps, touched,
+                                           unit_panel, unit_step, n_units, idesc_no_n, status_word);
     BSP_LAUNCH_CHECK();
     return BSP_OK;
 }
 
-template <typename T, int BS>
+#define BSP_LAUNCH_ARGS ma, mb, n_a, n_b, out, panel_first, step_off, steps, touched, unit_panel, unit_step, n_units, dtype, status_word, stream
+
+template <typename T, int BS, int G>
 int launch_op(int op, const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_t n_b, void* out,
-              const int32_t* offsets, const int32_t* pairs, const int32_t* chunk_begin, int32_t n_chunks,
-              int dtype, int32_t* status_word, cudaStream_t stream) {
+              const int32_t* panel_first, const int32_t* step_off, const int32_t* steps, const int32_t* touched,
+              const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units, int dtype,
+              int32_t* status_word, cudaStream_t stream) {
     switch (op) {
-        case BSP_OP_NN: return launch_cfg<T, BS, BSP_OP_NN>(ma, mb, n_a, n_b, out, offsets, pairs, chunk_begin, n_chunks, dtype, status_word, stream);
-        case BSP_OP_NT: return launch_cfg<T, BS, BSP_OP_NT>(ma, mb, n_a, n_b, out, offsets, pairs, chunk_begin, n_chunks, dtype, status_word, stream);
-        case BSP_OP_TN: return launch_cfg<T, BS, BSP_OP_TN>(ma, mb, n_a, n_b, out, offsets, pairs, chunk_begin, n_chunks, dtype, status_word, stream);
+        case BSP_OP_NN: return launch_cfg<T, BS, BSP_OP_NN, G>(BSP_LAUNCH_ARGS);
+        case BSP_OP_NT: return launch_cfg<T, BS, BSP_OP_NT, G>(BSP_LAUNCH_ARGS);
+        case BSP_OP_TN: return launch_cfg<T, BS, BSP_OP_TN, G>(BSP_LAUNCH_ARGS);
         default: return BSP_ERR_INVALID_ARG;
     }
+}
+
+template <typename T>
+int launch_shape(int bs, int width, int op, const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_t n_b,
+                 void* out, const int32_t* panel_first, const int32_t* step_off, const int32_t* steps,
+                 const int32_t* touched, const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units,
+                 int dtype, int32_t* status_word, cudaStream_t stream) {
+    if (bs == 64 && width == 1) return launch_op<T, 64, 1>(op, BSP_LAUNCH_ARGS);
+    if (bs == 64 && width == 2) return launch_op<T, 64, 2>(op, BSP_LAUNCH_ARGS);
+    if (bs == 128 && width == 1) return launch_op<T, 128, 1>(op, BSP_LAUNCH_ARGS);
+    if (bs == 128 && width == 2) return launch_op<T, 128, 2>(op, BSP_LAUNCH_ARGS);
+    return BSP_ERR_UNSUPPORTED;
 }
 
 }  // namespace
@@ -399,34 +512,44 @@ bool umma_applicable(int dtype, int bs) {
     return (dtype == BSP_F16 || dtype == BSP_BF16) && (bs == 64 || bs == 128);
 }
 
-int umma_num_chunks(int dtype, int bs) {
-    if (!umma_applicable(dtype, bs)) return 0;
-    return num_sms() * (bs == 64 ? Cfg<64>::kCtasPerSm : Cfg<128>::kCtasPerSm);
+}  // namespace bsp
+
+using namespace bsp;
+
+extern "C" int bsp_umma_max_width(int dtype, int bs) {
+    return umma_applicable(dtype, bs) ? 2 : 0;
 }
 
-int launch_matmul_umma(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
-                       int64_t n_out, const int32_t* offsets, const int32_t* pairs,
-                       const int32_t* chunk_begin, int32_t n_chunks, int bs, int dtype, int op,
-                       int32_t* status_word, cudaStream_t stream) {
-    if (!umma_applicable(dtype, bs)) return BSP_ERR_UNSUPPORTED;
-    if (!chunk_begin || n_chunks < 1 || n_a < 1 || n_b < 1) return BSP_ERR_INVALID_ARG;
-    // TMA coordinates are 32-bit row indices into the (n_blocks * bs)-row view.
-    if (n_a * bs > 0x7fffffffLL || n_b * bs > 0x7fffffffLL || n_out > 0x7fffffffLL)
-        return BSP_ERR_UNSUPPORTED;
+extern "C" int bsp_umma_num_ctas(int dtype, int bs, int width) {
+    if (!umma_applicable(dtype, bs) || (width != 1 && width != 2)) return 0;
+    const int per_sm = bs == 64 ? (width == 1 ? PCfg<64, 1>::kCtasPerSm : PCfg<64, 2>::kCtasPerSm)
+                                : (width == 1 ? PCfg<128, 1>::kCtasPerSm : PCfg<128, 2>::kCtasPerSm);
+    return umma::num_sms() * per_sm;
+}
+
+extern "C" int bsp_matmul_umma(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out, int64_t n_out,
+                               const int32_t* panel_first, int64_t n_panels, const int32_t* step_off,
+                               const int32_t* steps, const int32_t* touched, const int32_t* unit_panel,
+                               const int32_t* unit_step, int32_t n_units, int width, int bs, int dtype, int op,
+                               int32_t* status_word, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (n_a < 1 || n_b < 1 || n_out < 0 || n_panels < 0) return BSP_ERR_INVALID_ARG;
+    if (!umma_applicable(dtype, bs) || (width != 1 && width != 2)) return BSP_ERR_UNSUPPORTED;
+    if (op != BSP_OP_NN && op != BSP_OP_NT && op != BSP_OP_TN) return BSP_ERR_INVALID_ARG;
+    if (n_out == 0 || n_panels == 0) return BSP_OK;
+    if (!a || !b || !out || !panel_first || !step_off || !steps || !touched || !unit_panel || !unit_step ||
+        n_units < 1)
+        return BSP_ERR_INVALID_ARG;
+    if (n_a * bs > 0x7fffffffLL || n_b * bs > 0x7fffffffLL || n_out > 0x7fffffffLL) return BSP_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) ||
-        (reinterpret_cast<uintptr_t>(out) & 15))
+        (reinterpret_cast<uintptr_t>(out) & 31) || (reinterpret_cast<uintptr_t>(steps) & 15))
         return BSP_ERR_INVALID_ARG;
     CUtensorMap ma, mb;
-    int st = make_block_map(&ma, a, n_a, bs, dtype);
+    // a block read MN-major is fetched 64 rows at a time, one read K-major as bs rows x 64 columns
+    int st = umma::make_block_map(&ma, a, n_a, bs, dtype, op == BSP_OP_TN ? 64 : bs);
     if (st != BSP_OK) return st;
-    st = make_block_map(&mb, b, n_b, bs, dtype);
+    st = umma::make_block_map(&mb, b, n_b, bs, dtype, op != BSP_OP_NT ? 64 : bs);
     if (st != BSP_OK) return st;
-    if (dtype == BSP_F16) {
-        if (bs == 64) return launch_op<__half, 64>(op, ma, mb, n_a, n_b, out, offsets, pairs, chunk_begin, n_chunks, dtype, status_word, stream);
-        return launch_op<__half, 128>(op, ma, mb, n_a, n_b, out, offsets, pairs, chunk_begin, n_chunks, dtype, status_word, stream);
-    }
-    if (bs == 64) return launch_op<__nv_bfloat16, 64>(op, ma, mb, n_a, n_b, out, offsets, pairs, chunk_begin, n_chunks, dtype, status_word, stream);
-    return launch_op<__nv_bfloat16, 128>(op, ma, mb, n_a, n_b, out, offsets, pairs, chunk_begin, n_chunks, dtype, status_word, stream);
+    if (dtype == BSP_F16) return launch_shape<__half>(bs, width, op, BSP_LAUNCH_ARGS);
+    return launch_shape<__nv_bfloat16>(bs, width, op, BSP_LAUNCH_ARGS);
 }
-
-}  // namespace bsp

@@ -46,14 +46,8 @@ class _MatmulPlans:
         return sl_x.size(1), sl_x.size(2), sl_y.size(2)  # R, K, C
 
 
-def _n_chunks(sparsity_block_size: int | None) -> int:
-    """Number of persistent CTAs (schedule chunks) the tcgen05 kernel uses for this block size."""
-    bs = 128 if sparsity_block_size == 128 else 64
-    return _cabi.lib().bsp_matmul_num_chunks(_cabi.DATA_DTYPE_CODES[torch.bfloat16], bs, _cabi.KERNEL_AUTO)
-
-
 def matmul_build_layout_cache(layout_cache: dict | None, sparsity_layout_x: Tensor, sparsity_layout_y: Tensor,
-                              sparsity_layout_output: Tensor, sparsity_block_size: int | None = None) -> dict:
+                              sparsity_layout_output: Tensor) -> dict:
     """Builds or reuses the matmul metadata (blksprs/ops/matmul.py:256-279 plus the pair plans)."""
     layout_cache = prepare_layout_cache(layout_cache, "matmul", sparsity_layout_x, sparsity_layout_y,
                                         sparsity_layout_output)
@@ -70,14 +64,10 @@ def matmul_build_layout_cache(layout_cache: dict | None, sparsity_layout_x: Tens
     if _PLANS not in layout_cache:
         layout_cache[_PLANS] = _MatmulPlans(sparsity_layout_x, sparsity_layout_y, sparsity_layout_output)
     plans: _MatmulPlans = layout_cache[_PLANS]
-    chunks = _n_chunks(sparsity_block_size)
-    if plans.forward is not None and plans.forward.n_chunks != chunks:
-        plans.forward = plans.grad_x = plans.grad_y = None  # same layouts, other block size class
     if plans.forward is None:
         R, K, C = plans.dims()
         plans.forward = Product(_cabi.OP_NN, layout_cache["layout_indices_o"],
-                                        layout_cache["packed_indices_x"], layout_cache["packed_indices_y"],
-                                        R, K, C, chunks)
+                                layout_cache["packed_indices_x"], layout_cache["packed_indices_y"], R, K, C)
 
     validate_contiguous(sparsity_layout_x, layout_cache["packed_indices_x"],
                         sparsity_layout_y, layout_cache["packed_indices_y"],
@@ -93,13 +83,12 @@ def _backward_plans(plans: _MatmulPlans, packed_x: Tensor, packed_y: Tensor, n_x
     R, K, C = plans.dims()
     if plans.packed_o is None:
         plans.packed_o = build_packed_indices(sl_o)
-    chunks = plans.forward.n_chunks
     if plans.grad_x is None:
         lut_x = build_layout_indices(sl_x, n_x)
-        plans.grad_x = Product(_cabi.OP_NT, lut_x, plans.packed_o, packed_y, R, K, C, chunks)
+        plans.grad_x = Product(_cabi.OP_NT, lut_x, plans.packed_o, packed_y, R, K, C)
     if plans.grad_y is None:
         lut_y = build_layout_indices(sl_y, n_y)
-        plans.grad_y = Product(_cabi.OP_TN, lut_y, packed_x, plans.packed_o, R, K, C, chunks)
+        plans.grad_y = Product(_cabi.OP_TN, lut_y, packed_x, plans.packed_o, R, K, C)
 
 
 class _BlockSparseMatmul(torch.autograd.Function):
@@ -160,7 +149,7 @@ def _matmul_eager(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_ou
     validate_sparsity_block_size(sparsity_block_size, x, y)
 
     layout_cache = matmul_build_layout_cache(layout_cache, sparsity_layout_x, sparsity_layout_y,
-                                             sparsity_layout_output, sparsity_block_size)
+                                             sparsity_layout_output)
     plans = layout_cache[_PLANS]
     if plans.n_x is None and validation_enabled():
         # validate_sparsity has just confirmed these against the layouts

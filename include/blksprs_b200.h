@@ -67,13 +67,6 @@ enum {
 /* output-layout inference rule */
 enum { BSP_LAYOUT_EXACT = 0, BSP_LAYOUT_FAST = 1, BSP_LAYOUT_OUTER = 2 };
 
-/* kernel family selector for bsp_matmul */
-enum {
-    BSP_KERNEL_AUTO = 0, /* tcgen05 for 16-bit data and bs >= 64, mma.sync otherwise */
-    BSP_KERNEL_MMA = 1,  /* force the mma.sync kernel (any dtype, any bs)            */
-    BSP_KERNEL_UMMA = 2  /* force the tcgen05 kernel (error if not applicable)       */
-};
-
 /* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
 int bsp_version(void);
 
@@ -195,51 +188,46 @@ int bsp_plan_fill(const int64_t* lut_out, int64_t n_out,
                   const int64_t* packed_b, int64_t b_sb, int64_t b_st, int64_t b_sc,
                   int64_t T, const int32_t* offsets, int32_t* pairs_out, void* stream);
 
-/* Splits the n_out output blocks into `n_chunks` contiguous ranges of nearly
- * equal cost (cost of a block = its pair count + `block_cost`);
- * chunk_begin_out is int32 (n_chunks+1). */
+/* Splits n_out items (output blocks or panels, with CSR `offsets` of their pairs
+ * or steps) into `n_chunks` contiguous ranges of nearly equal cost (cost of an
+ * item = its count + `block_cost`); chunk_begin_out is int32 (n_chunks+1). */
 int bsp_plan_schedule(const int32_t* offsets, int64_t n_out, int32_t block_cost,
                       int32_t n_chunks, int32_t* chunk_begin_out, void* stream);
 
 /* ---- block-sparse matmul ---------------------------------------------- */
 
-/* Number of persistent CTAs bsp_matmul launches for the tcgen05 kernel on the
- * current device (= the `n_chunks` a schedule for it must have); 0 when
- * the (dtype, bs) pair is served by the mma.sync kernel. */
-int bsp_matmul_num_chunks(int dtype, int bs, int kernel);
-
-/* Block-sparse product on a pair plan.  Replaces matmul_forward + matmul_kernel,
- * blksprs/ops/matmul.py:70-127,148-253 (op = BSP_OP_NN), and the two products
- * of matmul_wrapper_backward, blksprs/ops/matmul.py:130-145 (BSP_OP_NT,
- * BSP_OP_TN), without materialising the transposes of ops/transpose.py.
+/* Block-sparse product on a pair plan with warp-level mma.sync instructions:
+ * any block size >= 16, fp16 / bf16 / fp32 (TF32).  Replaces matmul_forward +
+ * matmul_kernel, blksprs/ops/matmul.py:70-127,148-253 (op = BSP_OP_NN), and the
+ * two products of matmul_wrapper_backward, blksprs/ops/matmul.py:130-145
+ * (BSP_OP_NT, BSP_OP_TN), without materialising the transposes of
+ * ops/transpose.py.
  *   a, b       compressed operands (n_a, bs, bs), (n_b, bs, bs) of `dtype`
  *   out        compressed result (n_out, bs, bs) of `dtype`; every block is
  *              written (zeros where a block has no pair); fp32 accumulation
  *   offsets    int32 (n_out+1), pairs int32 (total,2)
- *   chunk_begin int32 (n_chunks+1) from bsp_plan_schedule (tcgen05 kernel
- *              only; may be null for the mma.sync kernel)
  *   status_word device int32[1] or null: receives BSP_ERR_DEVICE_* when a
  *              kernel meets an out-of-range index or a wait limit; never
  *              cleared by the kernel. */
-int bsp_matmul(const void* a, int64_t n_a, const void* b, int64_t n_b,
-               void* out, int64_t n_out,
-               const int32_t* offsets, const int32_t* pairs,
-               const int32_t* chunk_begin, int32_t n_chunks,
-               int bs, int dtype, int op, int kernel,
-               int32_t* status_word, void* stream);
+int bsp_matmul_mma(const void* a, int64_t n_a, const void* b, int64_t n_b,
+                   void* out, int64_t n_out,
+                   const int32_t* offsets, const int32_t* pairs,
+                   int bs, int dtype, int op, int32_t* status_word, void* stream);
 
-/* ---- wide-N ("panel") variant of the tcgen05 kernel ----------------------
- * A panel is a run of up to bsp_panel_width() output blocks, consecutive in the
- * output LUT and in the same (batch, row) of the output layout.  The reference
- * kernel (blksprs/ops/matmul.py:148-253) re-loads the x tile for every output
- * tile of a row; here one staged A block serves the whole panel and the panel's
- * B blocks are multiplied by one wide MMA.  Same results as bsp_matmul. */
+/* ---- tcgen05 kernel and its step plan ------------------------------------
+ * For fp16 / bf16 and bs 64 / 128 the same products run on tcgen05 tensor
+ * cores from a step plan.  A panel is a run of up to `width` (1 or 2) output
+ * blocks, consecutive in the output LUT and in the same (batch, row) of the
+ * output layout.  The reference kernel (blksprs/ops/matmul.py:148-253) re-loads
+ * the x tile for every output tile of a row; here one staged A block serves the
+ * whole panel and the panel's B blocks are multiplied by one wide MMA. */
 
-/* Output blocks per panel for this (dtype, bs); 0 if the kernel does not apply. */
-int bsp_panel_width(int dtype, int bs);
+/* Largest panel width for this (dtype, bs); 0 if the tcgen05 kernel does not apply. */
+int bsp_umma_max_width(int dtype, int bs);
 
-/* Number of persistent CTAs (= schedule chunks, counted in panels). */
-int bsp_matmul_panel_num_chunks(int dtype, int bs);
+/* Number of persistent CTAs the tcgen05 kernel launches at most for this shape
+ * on the current device (callers size their unit schedule as a multiple of it). */
+int bsp_umma_num_ctas(int dtype, int bs, int width);
 
 /* counts_out[p] (int32) = number of steps of panel p (inner indices t whose A
  * block exists and that hit at least one B block of the panel); touched_out[p]
@@ -261,15 +249,17 @@ int bsp_panel_fill(const int64_t* lut_out, const int32_t* panel_first, int64_t n
                    const int64_t* packed_b, int64_t b_sb, int64_t b_st, int64_t b_sc,
                    int64_t T, const int32_t* step_offsets, int32_t* steps_out, void* stream);
 
-/* Block-sparse product on a panel plan (fp16 / bf16, bs 64 / 128).  chunk_begin
- * (int32, n_chunks+1) splits the panels among the persistent CTAs
- * (bsp_plan_schedule on step_offsets). */
-int bsp_matmul_panel(const void* a, int64_t n_a, const void* b, int64_t n_b,
-                     void* out, int64_t n_out,
-                     const int32_t* panel_first, int64_t n_panels,
-                     const int32_t* step_offsets, const int32_t* steps, const int32_t* touched,
-                     const int32_t* chunk_begin, int32_t n_chunks,
-                     int bs, int dtype, int op, int32_t* status_word, void* stream);
+/* Block-sparse product on a step plan.  Same result contract as bsp_matmul_mma.
+ *   unit_panel  int32 (n_units+1): the panels split into contiguous units of
+ *               about equal cost (bsp_plan_schedule on step_offsets); CTA c of
+ *               the launch works on units c, c + n_ctas, ...
+ *   unit_step   int32 (n_units+1): step_offsets[unit_panel[u]] */
+int bsp_matmul_umma(const void* a, int64_t n_a, const void* b, int64_t n_b,
+                    void* out, int64_t n_out,
+                    const int32_t* panel_first, int64_t n_panels,
+                    const int32_t* step_offsets, const int32_t* steps, const int32_t* touched,
+                    const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units,
+                    int width, int bs, int dtype, int op, int32_t* status_word, void* stream);
 
 /* Compressed transpose.  Replaces transpose_forward + flow_pull_kernel,
  * blksprs/ops/transpose.py:45-51, blksprs/ops/flow.py:64-111:

@@ -19,7 +19,7 @@ def declared_symbols():
 def test_header_declares_entry_points():
     names = declared_symbols()
     for must in ("bsp_build_packed_indices", "bsp_build_layout_indices", "bsp_layout_matmul", "bsp_plan_fill",
-                 "bsp_matmul", "bsp_transpose_blocks"):
+                 "bsp_matmul_mma", "bsp_matmul_umma", "bsp_panel_fill", "bsp_transpose_blocks"):
         assert must in names
 
 
@@ -47,8 +47,11 @@ def test_no_compute_calls_needed_for_status_text():
 def test_argument_errors_are_reported_without_a_device():
     lib = _cabi.lib()
     # invalid enum / sizes are rejected before any CUDA call
-    assert lib.bsp_matmul(None, -1, None, 0, None, 0, None, None, None, 0, 64, 1, 0, 0, None, None) == _cabi.ERR_INVALID_ARG
-    assert lib.bsp_matmul(None, 0, None, 0, None, 0, None, None, None, 0, 48, 1, 0, 0, None, None) == _cabi.ERR_INVALID_ARG
-    assert lib.bsp_matmul(None, 0, None, 0, None, 0, None, None, None, 0, 64, 7, 0, 0, None, None) == _cabi.ERR_UNSUPPORTED
-    assert lib.bsp_matmul(None, 0, None, 0, None, 0, None, None, None, 0, 64, 1, 0, 0, None, None) == _cabi.OK
+    assert lib.bsp_matmul_mma(None, -1, None, 0, None, 0, None, None, 64, 1, 0, None, None) == _cabi.ERR_INVALID_ARG
+    assert lib.bsp_matmul_mma(None, 0, None, 0, None, 0, None, None, 48, 1, 0, None, None) == _cabi.ERR_INVALID_ARG
+    assert lib.bsp_matmul_mma(None, 0, None, 0, None, 0, None, None, 64, 7, 0, None, None) == _cabi.ERR_UNSUPPORTED
+    assert lib.bsp_matmul_mma(None, 0, None, 0, None, 0, None, None, 64, 1, 0, None, None) == _cabi.OK
+    assert lib.bsp_matmul_umma(None, 1, None, 1, None, 0, None, 0, None, None, None, None, None, 0, 2, 32, 1, 0,
+                               None, None) == _cabi.ERR_UNSUPPORTED
+    assert lib.bsp_umma_max_width(2, 64) == 0 and lib.bsp_umma_max_width(1, 64) == 2
     assert lib.bsp_layout_matmul(None, 0, None, 0, 1, 1, 1, 1, 9, None, None) == _cabi.ERR_INVALID_ARG

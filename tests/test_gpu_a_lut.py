@@ -121,5 +121,30 @@ def test_pair_plan_matches_oracle():
         last = np.zeros(len(pairs), dtype=bool)
         last[offs[1:][np.diff(offs) > 0] - 1] = True
         assert np.array_equal((got[:, 0] >> 30) & 1, last.astype(got.dtype))
-        cb = plan.chunk_begin.cpu().numpy()
-        assert cb[0] == 0 and cb[-1] == plan.n_out and np.all(np.diff(cb) >= 0)
+        # step plans: single-block steps reproduce the pairs; two-block panels cover them exactly
+        for width in (1, 2):
+            sp = product.step_plan(64, torch.bfloat16, width)
+            steps = sp.steps.cpu().numpy()[:sp.n_steps]
+            first = sp.panel_first.cpu().numpy()
+            so = sp.step_offsets.cpu().numpy()
+            up = sp.unit_panel.cpu().numpy()
+            assert up[0] == 0 and up[-1] == sp.n_panels and np.all(np.diff(up) >= 0)
+            assert np.array_equal(sp.unit_step.cpu().numpy(), so[up])
+            rebuilt = [[] for _ in range(plan.n_out)]
+            for pn in range(sp.n_panels):
+                g = first[pn + 1] - first[pn]
+                assert 1 <= g <= width
+                seen = 0
+                for s in range(so[pn], so[pn + 1]):
+                    a_blk, ctrl = steps[s, 0], steps[s, 5]
+                    present, fresh = ctrl & 0xF, (ctrl >> 4) & 0xF
+                    assert present != 0 and (present >> g) == 0 and fresh == (present & ~seen)
+                    assert bool(ctrl & 0x100) == (s == so[pn + 1] - 1) and ((ctrl >> 12) & 7) == g
+                    seen |= present
+                    for q in range(g):
+                        if (present >> q) & 1:
+                            rebuilt[first[pn] + q].append((a_blk, steps[s, 1 + q]))
+                assert seen == sp.touched.cpu().numpy()[pn]
+            flat = [p for blk in rebuilt for p in blk]
+            assert np.array_equal(np.array(flat).reshape(-1, 2), pairs)
+            assert [len(b) for b in rebuilt] == list(np.diff(offs))
