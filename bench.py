@@ -3,7 +3,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--config config2] [--impl ours|reference]
 
 One step = one forward product O = X·Y plus the two backward products dX = dO·Yᵀ, dY = Xᵀ·dO of
-the workload (three launches of the native matmul kernel on pre-built pair plans; LUTs and plans
+the workload (three launches of the native matmul kernel on pre-built plans; LUTs and plans
 are built before the timed region, as the reference's warm ``layout_cache`` would be).
 
 The default workload is the bf16 SDD case: X, Y (16, 2048, 2048), block 64, Bernoulli(0.25)

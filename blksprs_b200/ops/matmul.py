@@ -6,7 +6,7 @@ same validation errors, same layout-cache entries (``packed_indices_x``,
 tensors), same ``BlksprsTensor`` result.  The forward product and the two
 backward products (``dX = dO·Yᵀ`` on x's layout, ``dY = Xᵀ·dO`` on y's layout,
 blksprs/ops/matmul.py:130-145) each run as one launch of the native library on a
-pre-built pair plan; no transposed copy of an operand is ever materialised.
+pre-built plan; no transposed copy of an operand is ever materialised.
 """
 from __future__ import annotations
 
@@ -26,7 +26,7 @@ _PLANS = "_b200_plans"
 
 
 class _MatmulPlans:
-    """Private cache entry: pair plans and the extra LUTs the backward products need.
+    """Private cache entry: the plans of the three products and the extra LUTs the backward products need.
 
     Lives in the layout cache as one opaque value, so filling in the backward
     plans later does not change the cache's recorded state.
@@ -48,7 +48,7 @@ class _MatmulPlans:
 
 def matmul_build_layout_cache(layout_cache: dict | None, sparsity_layout_x: Tensor, sparsity_layout_y: Tensor,
                               sparsity_layout_output: Tensor) -> dict:
-    """Builds or reuses the matmul metadata (blksprs/ops/matmul.py:256-279 plus the pair plans)."""
+    """Builds or reuses the matmul metadata (blksprs/ops/matmul.py:256-279 plus the plans of the native kernels)."""
     layout_cache = prepare_layout_cache(layout_cache, "matmul", sparsity_layout_x, sparsity_layout_y,
                                         sparsity_layout_output)
 
