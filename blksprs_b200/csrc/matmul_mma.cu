@@ -61,11 +61,12 @@ __device__ inline void cp_async16(void* dst, const void* src) {
 __device__ inline void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ inline void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-__device__ inline uint32_t f32_to_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(r) : "f"(x));
-    return r;
-}
+// fp32 operands go to the TF32 tensor-core instruction as they are: the hardware reads the
+// upper 19 bits and drops the low 13 mantissa bits.  This is what the reference's `tl.dot` on
+// fp32 inputs does (blksprs/ops/matmul.py:242 with Triton's default input precision), and it makes
+// fp32 results identical to the reference's on the same GPU; rounding to nearest instead would be
+// closer to IEEE fp32 but about 1e-3 * max|ref| away from the reference.
+__device__ inline uint32_t f32_to_tf32(float x) { return __float_as_uint(x); }
 __device__ inline void ldmatrix_x4(uint32_t* r, const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
