@@ -406,40 +406,77 @@ def run_gpu_arm(args):
     fwd_ms = f0.elapsed_time(f1) / args.steps
 
     # ---- end to end through the public op, host buffers in and out -------------------------
+    # Every step copies its three pinned host inputs to the device, runs ops.matmul + backward and
+    # copies all three results back to pinned host memory.  The copies run on their own streams,
+    # two buffer slots deep, so the upload of step i+1 and the download of step i-1 overlap step i
+    # (the PCIe link is full duplex); nothing is skipped.
     host_sets = [tuple(t.cpu().pin_memory() for t in s) for s in sets[:2]]
-    host_out = None
     layout_cache = {}
     h2d = sum(t.numel() * t.element_size() for t in host_sets[0])
+    dev_in = [tuple(torch.empty_like(t, device=dev) for t in host_sets[0]) for _ in range(2)]
+    host_out = [None, None]
+    keep = [None, None]
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_done = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    main = torch.cuda.current_stream(dev)
     d2h = 0
+    issued = 0
 
     def e2e_step(i):
-        nonlocal host_out, d2h
-        hx, hy, hg = host_sets[i % 2]
-        x = hx.to(dev, non_blocking=True).requires_grad_(True)
-        y = hy.to(dev, non_blocking=True).requires_grad_(True)
-        g = hg.to(dev, non_blocking=True)
+        nonlocal d2h, issued
+        slot = i % 2
+        with torch.cuda.stream(s_in):
+            if issued >= 2:
+                s_in.wait_event(ev_done[slot])       # step i-2 has finished reading this slot
+            for dst, src in zip(dev_in[slot], host_sets[slot]):
+                dst.copy_(src, non_blocking=True)
+            ev_in[slot].record(s_in)
+        main.wait_event(ev_in[slot])
+        x = dev_in[slot][0].detach().requires_grad_(True)
+        y = dev_in[slot][1].detach().requires_grad_(True)
         out = bs.ops.matmul(x, lxd, y, lyd, lod, bsz, layout_cache)
-        out.backward(g)
+        out.backward(dev_in[slot][2])
         res = (out.detach(), x.grad, y.grad)
-        if host_out is None:
-            host_out = tuple(torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in res)
+        ev_done[slot].record(main)
+        if host_out[slot] is None:
+            host_out[slot] = tuple(torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in res)
             d2h = sum(t.numel() * t.element_size() for t in res)
-        for dst, src in zip(host_out, res):
-            dst.copy_(src, non_blocking=True)
-        torch.cuda.synchronize()
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_done[slot])
+            for dst, src in zip(host_out[slot], res):
+                dst.copy_(src, non_blocking=True)
+                src.record_stream(s_out)
+            ev_out[slot].record(s_out)
+        keep[slot] = res
+        issued += 1
+        if issued >= 2:
+            ev_out[1 - slot].synchronize()           # bound the host's run-ahead to two steps
+
+    def e2e_drain():
+        main.wait_stream(s_out)
+        main.wait_stream(s_in)
 
     e2e_steps = 0 if args.kernel_only else args.steps
     for i in range(min(args.warmup, 3) if e2e_steps else 0):
         e2e_step(i)
+    e2e_drain()
     g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     g0.record()
     for i in range(e2e_steps):
         e2e_step(i)
+    e2e_drain()
     g1.record()
     barrier()
     e2e_s = g0.elapsed_time(g1) * 1e-3
     check_device_status(dev)
+    if e2e_steps and rank == 0:
+        # the last step's results really are on the host
+        last = (e2e_steps - 1) % 2
+        ref_out = plans.forward.run(sets[last][0], sets[last][1], bsz)
+        assert torch.equal(host_out[last][0], ref_out.cpu()), "end-to-end result differs from the device-resident run"
 
     # ---- reduce over ranks -------------------------------------------------------------------
     stats = torch.tensor([ms, e2e_s * 1e3, fwd_ms], dtype=torch.float64, device=dev)
