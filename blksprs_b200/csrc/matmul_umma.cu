@@ -153,45 +153,60 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     if ((int)blockIdx.x < n_units) {
         if (warp == 0) {
             // ---------------- producer: lane l owns ring stage l ----------------
-            // ring entry = (step, k-chunk); absolute entry index = step * KC + k-chunk
-            const int4* recs = reinterpret_cast<const int4*>(steps);
-            auto unit_range = [&](int uu, int& b, int& e) {
-                if (uu < n_units) {
-                    b = unit_step[uu] * KC;
-                    e = unit_step[uu + 1] * KC;
-                } else {
-                    b = e = 0;
-                }
-            };
-            auto load_rec = [&](int pos, int end, int4& r0, int4& r1) {
-                const int e = pos + lane;
-                if (lane < S && e < end) {
+            // ring entry = (step, k-chunk); absolute entry index = step * KC + k-chunk.  Inside a unit
+            // lane l fills entries l, l + S, ...; every lane runs its own loop, so a stage is refilled
+            // as soon as the MMA issuer has released it, whatever the other stages are doing.
+            if (lane < S) {
+                const int4* recs = reinterpret_cast<const int4*>(steps);
+                auto unit_range = [&](int uu, int& b, int& e) {
+                    if (uu < n_units) {
+                        b = unit_step[uu] * KC;
+                        e = unit_step[uu + 1] * KC;
+                    } else {
+                        b = e = 0;
+                    }
+                };
+                auto load_rec = [&](int e, int4& r0, int4& r1) {
                     const int64_t i = e / KC;
                     r0 = recs[2 * i];
                     r1 = recs[2 * i + 1];
-                } else {
-                    r0 = make_int4(0, -1, -1, -1);
-                    r1 = make_int4(-1, 0, 0, 0);
+                };
+                int u = blockIdx.x, ub, ue, nub, nue;
+                unit_range(u, ub, ue);
+                unit_range(u + gridDim.x, nub, nue);
+                int e = ub + lane;
+                int4 c0 = make_int4(0, 0, 0, 0), c1 = c0, n0 = c0, n1 = c0;
+                bool have = false;
+                if (e < ue) {
+                    load_rec(e, c0, c1);
+                    have = true;
                 }
-            };
-            int u = blockIdx.x, ub, ue, nub, nue;
-            unit_range(u, ub, ue);
-            unit_range(u + gridDim.x, nub, nue);
-            int pos = ub;
-            int4 c0, c1, n0, n1;
-            load_rec(pos, ue, c0, c1);
-            uint32_t uses = 0;  // how often this lane's stage has been filled
-            bool alive = true;
-            PROF_DECL(w_empty);
-            PROF_T0(t_start);
-            while (u < n_units && alive) {
-                // where the next round starts: further into this unit, or the next unit's head
-                int npos, nend;
-                const bool unit_done = pos + S >= ue;
-                if (!unit_done) { npos = pos + S; nend = ue; } else { npos = nub; nend = nue; }
-                load_rec(npos, nend, n0, n1);
-                if (lane < S && pos + lane < ue) {
-                    const int kc = (pos + lane) % KC;
+                uint32_t uses = 0;  // how often this lane's stage has been filled
+                bool alive = true;
+                PROF_DECL(w_empty);
+                PROF_T0(t_start);
+                while (u < n_units && alive) {
+                    if (e >= ue) {  // nothing (left) for this lane in the unit
+                        u += gridDim.x;
+                        ub = nub;
+                        ue = nue;
+                        unit_range(u + gridDim.x, nub, nue);
+                        e = ub + lane;
+                        have = false;
+                        continue;
+                    }
+                    if (!have) load_rec(e, c0, c1);
+                    // fetch this lane's next record now: later in this unit, or its first in the next
+                    const int ne = e + S;
+                    bool nhave = false;
+                    if (ne < ue) {
+                        load_rec(ne, n0, n1);
+                        nhave = true;
+                    } else if (nub + lane < nue) {
+                        load_rec(nub + lane, n0, n1);
+                        nhave = true;
+                    }
+                    const int kc = e % KC;
                     int ia = c0.x;
                     int ib[4] = {c0.y, c0.z, c0.w, c1.x};
                     const uint32_t ctrl = (uint32_t)c1.y;
@@ -252,21 +267,23 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             }
                         }
                     }
+                    if (ne < ue) {
+                        e = ne;
+                    } else {
+                        u += gridDim.x;
+                        ub = nub;
+                        ue = nue;
+                        unit_range(u + gridDim.x, nub, nue);
+                        e = ub + lane;
+                    }
+                    have = nhave;
+                    c0 = n0;
+                    c1 = n1;
                 }
-                alive = __all_sync(0xffffffffu, alive);
-                if (unit_done) {
-                    u += gridDim.x;
-                    ub = nub;
-                    ue = nue;
-                    unit_range(u + gridDim.x, nub, nue);
+                if (lane == 0) {
+                    PROF_STORE(0, clock64() - t_start);
+                    PROF_STORE(1, w_empty);
                 }
-                pos = npos;
-                c0 = n0;
-                c1 = n1;
-            }
-            if (lane == 0) {
-                PROF_STORE(0, clock64() - t_start);
-                PROF_STORE(1, w_empty);
             }
         } else if (warp == 1) {
             // ---------------- MMA issuer ----------------
