@@ -36,12 +36,12 @@ MAX_UNITS_PER_CTA = int(os.environ.get("BLKSPRS_B200_MAX_UNITS", "64"))
 KERNELS = ("auto", "mma", "umma", "panel")
 _kernel_choice = os.environ.get("BLKSPRS_B200_KERNEL", "auto")
 
-# "auto" uses panels of two output blocks for block size 64 when they merge enough work: steps /
-# pairs at or below this ratio (0.5 = every step serves two (A, B) pairs).  Measured on B200:
-# dense-B products (P*V, dO*V^T on an attention layout) gain 1.25-1.35x, random x random layouts
-# (ratio ~0.85) lose, and for block size 128 single-block steps are already at the L2/HBM limits.
+# "auto" uses panels of two output blocks when they merge enough work: steps / pairs at or below
+# this ratio (0.5 = every step serves two (A, B) pairs).  Measured on B200: dense-B products (P*V,
+# dO*V^T on an attention layout, sparse x dense at block size 128) gain 1.15-1.35x, random x random
+# layouts (ratio ~0.85) lose.
 PANEL_STEP_RATIO = float(os.environ.get("BLKSPRS_B200_PANEL_RATIO", "0.58"))
-PANEL_AUTO_BLOCK_SIZES = (64,)
+PANEL_AUTO_BLOCK_SIZES = (64, 128)
 
 
 def set_kernel(name: str) -> None:
