@@ -39,8 +39,9 @@ METRIC = "block-sparse matmul effective TFLOP/s (nnz-block FLOPs), forward+backw
 N_BUFFER_SETS = 4
 
 # DRAM bytes (read + write) of one forward launch of the default workload (config2), from the ncu
-# capture summarised in profiles/matmul_umma_kernel_config2.md: 101.5 MB read + 82.7 MB written.
-FWD_KERNEL_DRAM_TRAFFIC_BYTES = {"config2": 184.2e6}
+# capture summarised in profiles/matmul_umma_kernel_config2.md: 71.7 MB read + 73.1 MB written (the
+# capture replays one launch on the same buffers, so part of the data is served from L2).
+FWD_KERNEL_DRAM_TRAFFIC_BYTES = {"config2": 144.8e6}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -405,6 +406,27 @@ def run_gpu_arm(args):
     torch.cuda.synchronize()
     fwd_ms = f0.elapsed_time(f1) / args.steps
 
+    # ---- the public op on device-resident tensors (what the reference's own timing measures) ----
+    api_cache = {}
+
+    def api_step(i):
+        x, y, g = sets[i % N_BUFFER_SETS]
+        x = x.detach().requires_grad_(True)
+        y = y.detach().requires_grad_(True)
+        bs.ops.matmul(x, lxd, y, lyd, lod, bsz, api_cache).backward(g)
+
+    api_steps = 0 if args.kernel_only else args.steps
+    for i in range(3 if api_steps else 0):
+        api_step(i)
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a0.record()
+    for i in range(api_steps):
+        api_step(i)
+    a1.record()
+    torch.cuda.synchronize()
+    api_ms = a0.elapsed_time(a1) / max(api_steps, 1)
+
     # ---- end to end through the public op, host buffers in and out -------------------------
     # Every step copies its three pinned host inputs to the device, runs ops.matmul + backward and
     # copies all three results back to pinned host memory.  The copies run on their own streams,
@@ -513,6 +535,8 @@ def run_gpu_arm(args):
             },
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / max(e2e_steps, 1)},
+            "api": {"ms_per_step": api_ms if api_steps else None,
+                    "what": "ops.matmul + backward on device tensors, warm layout cache, validation on"},
             "gpu_launches": 3 * args.steps,
             "clocks": clocks.summary(),
         }
