@@ -15,14 +15,16 @@
 // transposed products of the backward pass (BSP_OP_NT, BSP_OP_TN) use the same staged data;
 // only the major-ness bits of the shared-memory and instruction descriptors change.
 //
-// Persistent CTAs (1 to 3 per SM), roles by warp:
-//   warp 0      producer: lane l owns ring stage l, polls that stage's "empty" barrier and
-//               issues the TMA copies of its entry (128-byte swizzle) as soon as it is free
-//   warp 1      MMA issuer: one thread issues four tcgen05.mma (K = 16 each) per run and entry,
-//               releases the stage with tcgen05.commit, and hands a finished accumulator group
-//               (the G accumulators of a panel, adjacent tensor-memory columns) to the epilogue
-//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulators, convert, write the output blocks
-//               with 32-byte stores; blocks no step touched are written as zeros
+// Persistent CTAs (1 to 3 per SM) of S + 5 warps, S = ring stages:
+//   warps 0..S-1  producers: warp w owns ring stage w; one lane polls that stage's "empty"
+//                 barrier and issues the TMA copies of its entries (128-byte swizzle) as soon as
+//                 the stage is free, so the copies of different stages issue in parallel
+//   warp S        MMA issuer: converged warp, one elected lane issues four tcgen05.mma (K = 16
+//                 each) per run and entry, releases the stage with tcgen05.commit, and hands a
+//                 finished accumulator group (the G accumulators of a panel, adjacent
+//                 tensor-memory columns) to the epilogue
+//   warps S+1..S+4 epilogue: tcgen05.ld the fp32 accumulators, convert, write the output blocks
+//                 with 32-byte stores; blocks no step touched are written as zeros
 //
 // Every wait is bounded (about one second): a wait that runs out records
 // BSP_ERR_DEVICE_TIMEOUT in the status word, all roles leave their loops, outstanding copies
@@ -36,8 +38,11 @@ using namespace umma;
 
 namespace {
 
-constexpr int kThreads = 192;
 constexpr uint32_t kCtrlLast = 0x100u;
+
+#ifndef BSP_UMMA_KSPLIT
+#define BSP_UMMA_KSPLIT 0
+#endif
 
 #ifdef BSP_UMMA_PROFILE
 // Debug build only: per-CTA cycle counters (8 per CTA) read back by bsp_debug_read_prof.
@@ -57,16 +62,16 @@ __device__ long long g_prof[1024 * 8];
 // columns each) and resident CTAs per SM.  Shared memory: stages x (1 + G) x bs x 128 bytes.
 template <int BS, int G> struct PCfg;
 template <> struct PCfg<64, 1> {   // 3 x (4 x 16 KiB), 3 x 128 columns
-    static constexpr int kStages = 4, kGroups = 2, kCtasPerSm = 3;
+    static constexpr int kStages = 4, kGroups = 2, kCtasPerSm = 3, kThreads = 32 * (kStages + 5);
 };
 template <> struct PCfg<64, 2> {   // 2 x (4 x 24 KiB), 2 x 256 columns
-    static constexpr int kStages = 4, kGroups = 2, kCtasPerSm = 2;
+    static constexpr int kStages = 4, kGroups = 2, kCtasPerSm = 2, kThreads = 32 * (kStages + 5);
 };
 template <> struct PCfg<128, 1> {  // 6 x 32 KiB, 4 x 128 columns
-    static constexpr int kStages = 6, kGroups = 4, kCtasPerSm = 1;
+    static constexpr int kStages = 6, kGroups = 4, kCtasPerSm = 1, kThreads = 32 * (kStages + 5);
 };
 template <> struct PCfg<128, 2> {  // 4 x 48 KiB, 2 x 256 columns
-    static constexpr int kStages = 4, kGroups = 2, kCtasPerSm = 1;
+    static constexpr int kStages = 4, kGroups = 2, kCtasPerSm = 1, kThreads = 32 * (kStages + 5);
 };
 
 constexpr int tmem_cols_pow2(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
@@ -92,7 +97,7 @@ __device__ __forceinline__ uint64_t chunk_desc(uint32_t base, int kk) {
 }
 
 template <typename T, int BS, int OP, int G>
-__global__ void __launch_bounds__(kThreads, PCfg<BS, G>::kCtasPerSm)
+__global__ void __launch_bounds__(PCfg<BS, G>::kThreads, PCfg<BS, G>::kCtasPerSm)
 matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    int64_t n_a, int64_t n_b, T* __restrict__ out,
                    const int32_t* __restrict__ panel_first, const int32_t* __restrict__ step_off,
@@ -105,6 +110,11 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     constexpr bool A_MN = (OP == BSP_OP_TN);
     constexpr bool B_MN = (OP != BSP_OP_NT);
     constexpr int TMEM_COLS = tmem_cols_pow2(NG * G * BS);
+    // A 64-row accumulator occupies lanes 0-15 of every 32-lane tensor-memory subpartition, so a
+    // second one fits into lanes 16-31 of the same columns.  For bs = 64 the four k-steps of a
+    // ring entry alternate between the two: two independent MMA chains per output block instead
+    // of one; the epilogue adds the halves (they arrive in lanes 0-15 / 16-31 of one tcgen05.ld).
+    constexpr bool KSPLIT = BSP_UMMA_KSPLIT && BS == 64;
     static_assert(S <= 32 && G <= 4 && G * BS <= 256, "panel configuration out of range");
 
     extern __shared__ unsigned char smem_raw[];
@@ -136,7 +146,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async;" ::: "memory");
     }
-    if (warp == 1) {
+    if (warp == S) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_addr((const void*)tmem_base_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -151,12 +161,14 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     // operand blocks of one batch are used by all SMs at about the same time and stay in L2.
     // Inside a unit the i-th ring entry uses stage i % S; a stage's barrier parity is its use count.
     if ((int)blockIdx.x < n_units) {
-        if (warp == 0) {
-            // ---------------- producer: lane l owns ring stage l ----------------
+        if (warp < S) {
+            // ---------------- producers: warp w owns ring stage w ----------------
             // ring entry = (step, k-chunk); absolute entry index = step * KC + k-chunk.  Inside a unit
-            // lane l fills entries l, l + S, ...; every lane runs its own loop, so a stage is refilled
-            // as soon as the MMA issuer has released it, whatever the other stages are doing.
-            if (lane < S) {
+            // producer w fills entries w, w + S, ...; every producer is a warp of its own (one lane
+            // active), so the stages are refilled independently and the copy instructions of
+            // different stages issue in parallel.
+            if (lane == 0) {
+                const int slot = warp;
                 const int4* recs = reinterpret_cast<const int4*>(steps);
                 auto unit_range = [&](int uu, int& b, int& e) {
                     if (uu < n_units) {
@@ -174,7 +186,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 int u = blockIdx.x, ub, ue, nub, nue;
                 unit_range(u, ub, ue);
                 unit_range(u + gridDim.x, nub, nue);
-                int e = ub + lane;
+                int e = ub + slot;
                 int4 c0 = make_int4(0, 0, 0, 0), c1 = c0, n0 = c0, n1 = c0;
                 bool have = false;
                 if (e < ue) {
@@ -191,7 +203,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         ub = nub;
                         ue = nue;
                         unit_range(u + gridDim.x, nub, nue);
-                        e = ub + lane;
+                        e = ub + slot;
                         have = false;
                         continue;
                     }
@@ -202,8 +214,8 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     if (ne < ue) {
                         load_rec(ne, n0, n1);
                         nhave = true;
-                    } else if (nub + lane < nue) {
-                        load_rec(nub + lane, n0, n1);
+                    } else if (nub + slot < nue) {
+                        load_rec(nub + slot, n0, n1);
                         nhave = true;
                     }
                     const int kc = e % KC;
@@ -222,8 +234,8 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         for (int q = 0; q < 4; ++q) ib[q] = 0;
                     }
                     const uint32_t phase = uses & 1u;
-                    const uint32_t ebar = empty_bar + 8 * lane, fbar = full_bar + 8 * lane;
-                    const uint32_t sa = data + lane * L::kStageBytes;
+                    const uint32_t ebar = empty_bar + 8 * slot, fbar = full_bar + 8 * slot;
+                    const uint32_t sa = data + slot * L::kStageBytes;
                     const uint32_t sb = sa + L::kChunkBytes;
                     unsigned long long t0 = 0;
                     PROF_T0(tw);
@@ -232,8 +244,8 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             PROF_ADD(w_empty, tw);
                             // first-touch flags count for the step's first chunk only; the panel ends
                             // with the step's last chunk
-                            ctrl_slot[lane] = (ctrl & (kc == 0 ? ~0u : ~0xF0u)) & (kc == KC - 1 ? ~0u : ~kCtrlLast);
-                            armed[lane] = (int)phase;
+                            ctrl_slot[slot] = (ctrl & (kc == 0 ? ~0u : ~0xF0u)) & (kc == KC - 1 ? ~0u : ~kCtrlLast);
+                            armed[slot] = (int)phase;
                             mbar_arrive_expect_tx(fbar, (1 + __popc(present)) * L::kChunkBytes);
                             if (A_MN) {
 #pragma unroll
@@ -274,18 +286,18 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         ub = nub;
                         ue = nue;
                         unit_range(u + gridDim.x, nub, nue);
-                        e = ub + lane;
+                        e = ub + slot;
                     }
                     have = nhave;
                     c0 = n0;
                     c1 = n1;
                 }
-                if (lane == 0) {
+                if (slot == 0) {
                     PROF_STORE(0, clock64() - t_start);
                     PROF_STORE(1, w_empty);
                 }
             }
-        } else if (warp == 1) {
+        } else if (warp == S) {
             // ---------------- MMA issuer ----------------
             // The whole warp runs this loop converged and one elected lane issues each MMA / commit:
             // stage, descriptor and accumulator arithmetic is then warp-uniform (uniform registers)
@@ -297,6 +309,8 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 bool new_panel = true, alive = true;
                 PROF_DECL(w_full);
                 PROF_DECL(w_tempty);
+                PROF_DECL(w_issue);
+                PROF_DECL(w_commit);
                 PROF_T0(t_start);
                 int u = blockIdx.x;
                 int n_entries = (unit_step[u + 1] - unit_step[u]) * KC;
@@ -314,6 +328,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         if (!mbar_wait(full_bar + 8 * stage, (stage_parity >> stage) & 1u, abort_flag, status_word)) { alive = false; break; }
                         PROF_ADD(w_full, tw2);
                         stage_parity ^= 1u << stage;
+                        PROF_T0(t_a);
                         tc_fence_after();
                         const uint32_t ctrl = ctrl_slot[stage];
                         const uint32_t present = ctrl & 0xFu, first = (ctrl >> 4) & 0xFu;
@@ -324,9 +339,14 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             // a step is one (A, B) pair
                             const uint32_t idesc = idesc_no_n | ((uint32_t)(BS >> 3) << 17);
 #pragma unroll
-                            for (int kk = 0; kk < 4; ++kk) {
-                                tc_mma_f16_elect(d0, chunk_desc<BS, A_MN>(sa, kk), chunk_desc<BS, B_MN>(sb, kk), idesc,
-                                           ((first & 1u) && kk == 0) ? 0u : 1u);
+                            for (int i = 0; i < 4; ++i) {
+                                // KSPLIT: k-steps {0,1} and {2,3} go to two accumulators, issued alternately
+                                const int kk = KSPLIT ? ((i & 1) * 2 + (i >> 1)) : i;
+                                const uint32_t half = KSPLIT ? (uint32_t)(kk >> 1) : 0u;
+                                const bool chain_head = KSPLIT ? (kk & 1) == 0 : kk == 0;
+                                tc_mma_f16_elect(d0 + (half << 20), chunk_desc<BS, A_MN>(sa, kk),
+                                                 chunk_desc<BS, B_MN>(sb, kk), idesc,
+                                                 ((first & 1u) && chain_head) ? 0u : 1u);
                             }
                         } else {
                             // one MMA chain per run of present columns with equal "first" status
@@ -343,13 +363,19 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 // row, MN-major blocks are bs/64 atoms of 8 KiB each
                                 const uint32_t sbq = sb + (B_MN ? q0 * H * 8192 : q0 * L::kChunkBytes);
 #pragma unroll
-                                for (int kk = 0; kk < 4; ++kk) {
-                                    tc_mma_f16_elect(d0 + q0 * BS, chunk_desc<BS, A_MN>(sa, kk),
-                                               chunk_desc<BS, B_MN>(sbq, kk), idesc, (f && kk == 0) ? 0u : 1u);
+                                for (int i = 0; i < 4; ++i) {
+                                    const int kk = KSPLIT ? ((i & 1) * 2 + (i >> 1)) : i;
+                                    const uint32_t half = KSPLIT ? (uint32_t)(kk >> 1) : 0u;
+                                    const bool chain_head = KSPLIT ? (kk & 1) == 0 : kk == 0;
+                                    tc_mma_f16_elect(d0 + q0 * BS + (half << 20), chunk_desc<BS, A_MN>(sa, kk),
+                                                     chunk_desc<BS, B_MN>(sbq, kk), idesc, (f && chain_head) ? 0u : 1u);
                                 }
                             }
                         }
+                        PROF_ADD(w_issue, t_a);
+                        PROF_T0(t_b);
                         tc_commit_elect(empty_bar + 8 * stage);
+                        PROF_ADD(w_commit, t_b);
                         new_panel = false;
                         if (ctrl & kCtrlLast) {
                             tc_commit_elect(tfull_bar + 8 * grp);
@@ -364,6 +390,8 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 if (lane == 0) PROF_STORE(2, clock64() - t_start);
                 if (lane == 0) PROF_STORE(3, w_full);
                 if (lane == 0) PROF_STORE(4, w_tempty);
+                if (lane == 0) PROF_STORE(5, w_issue);
+                if (lane == 0) PROF_STORE(6, w_commit);
                 tc_commit_elect(drain_bar);
                 mbar_wait(drain_bar, 0, abort_flag, status_word);
             }
@@ -422,6 +450,13 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 uint32_t v[32];
                                 tc_ld32(taddr + c0, v);
                                 tc_wait_ld();
+                                if (KSPLIT) {
+                                    // lanes 16-31 hold the second partial accumulator of the same rows
+#pragma unroll
+                                    for (int i = 0; i < 32; ++i)
+                                        v[i] = __float_as_uint(__uint_as_float(v[i]) +
+                                                               __shfl_down_sync(0xffffffffu, __uint_as_float(v[i]), 16));
+                                }
                                 if (row_valid) {
                                     // 32 columns = 64 bytes of the row: two 32-byte stores, each a whole sector
                                     T* dst = o + (int64_t)row * BS + c0;
@@ -444,10 +479,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     }
                 }
             }
-            if (warp == 2 && lane == 0) {
-                PROF_STORE(5, clock64() - t_start);
-                PROF_STORE(6, w_tfull);
-            }
+            if (warp == S + 1 && lane == 0) PROF_STORE(7, w_tfull);
         }
     }
 
@@ -466,7 +498,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
     }
     __syncthreads();
-    if (warp == 1) {
+    if (warp == S) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
                      ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
@@ -484,7 +516,7 @@ int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_
     const uint32_t idesc_no_n = make_idesc(dtype, BS, OP) & ~(0x3Fu << 17);
     int ctas = num_sms() * PCfg<BS, G>::kCtasPerSm;
     if (ctas > n_units) ctas = n_units;
-    kern<<<ctas, kThreads, smem, stream>>>(ma, mb, n_a, n_b, (T*)out, panel_first, step_off, steps, touched,
+    kern<<<ctas, PCfg<BS, G>::kThreads, smem, stream>>>(ma, mb, n_a, n_b, (T*)out, panel_first, step_off, steps, touched,
                                            unit_panel, unit_step, n_units, idesc_no_n, status_word);
     BSP_LAUNCH_CHECK();
     return BSP_OK;
