@@ -40,10 +40,6 @@ namespace {
 
 constexpr uint32_t kCtrlLast = 0x100u;
 
-#ifndef BSP_UMMA_KSPLIT
-#define BSP_UMMA_KSPLIT 0
-#endif
-
 #ifdef BSP_UMMA_PROFILE
 // Debug build only: per-CTA cycle counters (8 per CTA) read back by bsp_debug_read_prof.
 __device__ long long g_prof[1024 * 8];
@@ -61,8 +57,14 @@ __device__ long long g_prof[1024 * 8];
 // Per (block size, panel width): ring depth, accumulator groups (of G x bs tensor-memory
 // columns each) and resident CTAs per SM.  Shared memory: stages x (1 + G) x bs x 128 bytes.
 template <int BS, int G> struct PCfg;
+#ifndef BSP_C641_STAGES
+#define BSP_C641_STAGES 4
+#define BSP_C641_GROUPS 2
+#define BSP_C641_CTAS 3
+#endif
 template <> struct PCfg<64, 1> {   // 3 x (4 x 16 KiB), 3 x 128 columns
-    static constexpr int kStages = 4, kGroups = 2, kCtasPerSm = 3, kThreads = 32 * (kStages + 5);
+    static constexpr int kStages = BSP_C641_STAGES, kGroups = BSP_C641_GROUPS, kCtasPerSm = BSP_C641_CTAS,
+                         kThreads = 32 * (kStages + 5);
 };
 template <> struct PCfg<64, 2> {   // 2 x (4 x 24 KiB), 2 x 256 columns
     static constexpr int kStages = 4, kGroups = 2, kCtasPerSm = 2, kThreads = 32 * (kStages + 5);
@@ -110,11 +112,6 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     constexpr bool A_MN = (OP == BSP_OP_TN);
     constexpr bool B_MN = (OP != BSP_OP_NT);
     constexpr int TMEM_COLS = tmem_cols_pow2(NG * G * BS);
-    // A 64-row accumulator occupies lanes 0-15 of every 32-lane tensor-memory subpartition, so a
-    // second one fits into lanes 16-31 of the same columns.  For bs = 64 the four k-steps of a
-    // ring entry alternate between the two: two independent MMA chains per output block instead
-    // of one; the epilogue adds the halves (they arrive in lanes 0-15 / 16-31 of one tcgen05.ld).
-    constexpr bool KSPLIT = BSP_UMMA_KSPLIT && BS == 64;
     static_assert(S <= 32 && G <= 4 && G * BS <= 256, "panel configuration out of range");
 
     extern __shared__ unsigned char smem_raw[];
@@ -339,14 +336,9 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             // a step is one (A, B) pair
                             const uint32_t idesc = idesc_no_n | ((uint32_t)(BS >> 3) << 17);
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                // KSPLIT: k-steps {0,1} and {2,3} go to two accumulators, issued alternately
-                                const int kk = KSPLIT ? ((i & 1) * 2 + (i >> 1)) : i;
-                                const uint32_t half = KSPLIT ? (uint32_t)(kk >> 1) : 0u;
-                                const bool chain_head = KSPLIT ? (kk & 1) == 0 : kk == 0;
-                                tc_mma_f16_elect(d0 + (half << 20), chunk_desc<BS, A_MN>(sa, kk),
-                                                 chunk_desc<BS, B_MN>(sb, kk), idesc,
-                                                 ((first & 1u) && chain_head) ? 0u : 1u);
+                            for (int kk = 0; kk < 4; ++kk) {
+                                tc_mma_f16_elect(d0, chunk_desc<BS, A_MN>(sa, kk), chunk_desc<BS, B_MN>(sb, kk), idesc,
+                                                 ((first & 1u) && kk == 0) ? 0u : 1u);
                             }
                         } else {
                             // one MMA chain per run of present columns with equal "first" status
@@ -363,12 +355,9 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 // row, MN-major blocks are bs/64 atoms of 8 KiB each
                                 const uint32_t sbq = sb + (B_MN ? q0 * H * 8192 : q0 * L::kChunkBytes);
 #pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    const int kk = KSPLIT ? ((i & 1) * 2 + (i >> 1)) : i;
-                                    const uint32_t half = KSPLIT ? (uint32_t)(kk >> 1) : 0u;
-                                    const bool chain_head = KSPLIT ? (kk & 1) == 0 : kk == 0;
-                                    tc_mma_f16_elect(d0 + q0 * BS + (half << 20), chunk_desc<BS, A_MN>(sa, kk),
-                                                     chunk_desc<BS, B_MN>(sbq, kk), idesc, (f && chain_head) ? 0u : 1u);
+                                for (int kk = 0; kk < 4; ++kk) {
+                                    tc_mma_f16_elect(d0 + q0 * BS, chunk_desc<BS, A_MN>(sa, kk),
+                                                     chunk_desc<BS, B_MN>(sbq, kk), idesc, (f && kk == 0) ? 0u : 1u);
                                 }
                             }
                         }
@@ -450,13 +439,6 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 uint32_t v[32];
                                 tc_ld32(taddr + c0, v);
                                 tc_wait_ld();
-                                if (KSPLIT) {
-                                    // lanes 16-31 hold the second partial accumulator of the same rows
-#pragma unroll
-                                    for (int i = 0; i < 32; ++i)
-                                        v[i] = __float_as_uint(__uint_as_float(v[i]) +
-                                                               __shfl_down_sync(0xffffffffu, __uint_as_float(v[i]), 16));
-                                }
                                 if (row_valid) {
                                     // 32 columns = 64 bytes of the row: two 32-byte stores, each a whole sector
                                     T* dst = o + (int64_t)row * BS + c0;
