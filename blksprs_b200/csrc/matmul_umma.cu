@@ -531,6 +531,20 @@ int launch_shape(int bs, int width, int op, const CUtensorMap& ma, const CUtenso
     return BSP_ERR_UNSUPPORTED;
 }
 
+// Self test of the bounded wait every role of the matmul kernel relies on: one thread waits on
+// an mbarrier nothing will ever arrive on, with a short limit, and must come back with
+// BSP_ERR_DEVICE_TIMEOUT in the status word instead of hanging.
+__global__ void wait_limit_selftest_kernel(unsigned long long limit_ns, int32_t* status_word) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_addr(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_wait_slow(smem_addr(&bar), 0, &abort_flag, status_word, limit_ns);
+    }
+}
+
 }  // namespace
 
 #ifdef BSP_UMMA_PROFILE
@@ -546,6 +560,13 @@ bool umma_applicable(int dtype, int bs) {
 }  // namespace bsp
 
 using namespace bsp;
+
+extern "C" int bsp_selftest_wait_limit(uint32_t limit_us, int32_t* status_word, void* stream_) {
+    if (!status_word || limit_us == 0 || limit_us > 100000) return BSP_ERR_INVALID_ARG;  // at most 0.1 s
+    wait_limit_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream_>>>((unsigned long long)limit_us * 1000ull, status_word);
+    BSP_LAUNCH_CHECK();
+    return BSP_OK;
+}
 
 extern "C" int bsp_umma_max_width(int dtype, int bs) {
     return umma_applicable(dtype, bs) ? 2 : 0;

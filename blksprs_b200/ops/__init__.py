@@ -1,5 +1,7 @@
-"""Operations on compressed block-sparse tensors (the matmul path)."""
+"""Operations on compressed block-sparse tensors (the matmul path and the ops around it)."""
+from .conversion import from_blksprs, to_blksprs, to_dense, to_dense_shaped, to_sparse, to_sparse_shaped
 from .matmul import matmul
 from .transpose import transpose
 
-__all__ = ["matmul", "transpose"]
+__all__ = ["from_blksprs", "matmul", "to_blksprs", "to_dense", "to_dense_shaped", "to_sparse", "to_sparse_shaped",
+           "transpose"]

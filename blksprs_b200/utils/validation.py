@@ -139,6 +139,27 @@ def validate_sparsity(sparsity_block_size: int, *pairs: tuple[Tensor, Tensor], c
             raise ValueError("Mismatch between sparsity layout and blocks")
 
 
+def validate_sparsity_dense(sparsity_block_size: int, *pairs: tuple[Tensor, Tensor]) -> None:
+    """Checks dense tensors against their layouts (blksprs/utils/validation.py:318-339)."""
+    if not validation_enabled():
+        return
+    for tensor, layout in pairs:
+        validate_layout_values(layout)
+        if tensor.device != layout.device:
+            raise ValueError("Tensor and sparsity layout must be on same device")
+        if not layout.is_contiguous():
+            raise ValueError("Sparsity layout must be contiguous")
+        if layout.dim() != 3:
+            raise ValueError("Sparsity layout must have exactly 3 dimensions")
+        if tensor.size(0) != layout.size(0):
+            raise ValueError("Tensor batch dimension does not match sparsity layout")
+        if tensor.size(-1) % sparsity_block_size or tensor.size(-2) % sparsity_block_size:
+            raise ValueError("Tensor sizes must be divisible by sparsity block size")
+        if (tensor.size(-1) // sparsity_block_size != layout.size(-1)
+                or tensor.size(-2) // sparsity_block_size != layout.size(-2)):
+            raise ValueError("Tensor not conforming to sparsity layout")
+
+
 def validate_sparsity_layout(*sparsity_layouts: Tensor) -> None:
     if not validation_enabled():
         return

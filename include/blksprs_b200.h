@@ -261,6 +261,13 @@ int bsp_matmul_umma(const void* a, int64_t n_a, const void* b, int64_t n_b,
                     const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units,
                     int width, int bs, int dtype, int op, int32_t* status_word, void* stream);
 
+/* Self test of the bounded device wait (no reference counterpart): launches one
+ * thread that waits at most `limit_us` (1..100000) microseconds on a barrier
+ * nothing arrives on; the kernel must return and leave BSP_ERR_DEVICE_TIMEOUT
+ * in `status_word` (device int32[1]).  The matmul kernels use the same wait
+ * with a limit of about one second. */
+int bsp_selftest_wait_limit(uint32_t limit_us, int32_t* status_word, void* stream);
+
 /* Compressed transpose.  Replaces transpose_forward + flow_pull_kernel,
  * blksprs/ops/transpose.py:45-51, blksprs/ops/flow.py:64-111:
  *   out[p] = x[src_index[p]]^T  for p in [0, n_out), where src_index (int64,
@@ -270,6 +277,25 @@ int bsp_matmul_umma(const void* a, int64_t n_a, const void* b, int64_t n_b,
 int bsp_transpose_blocks(const void* x, int64_t n_x, void* out, int64_t n_out,
                          const int64_t* src_index, int bs, int elem_bytes,
                          void* stream);
+
+/* ---- dense <-> compressed conversion ------------------------------------ */
+
+/* Dense -> compressed.  Replaces to_sparse_forward + to_sparse_kernel,
+ * blksprs/ops/conversion.py:191-276: out[p] = block (b, r, c) of the dense
+ * (B, rows, cols) tensor for the p-th row (b, r, c) of `lut` (int64 (n,3)).
+ * elem_bytes is 1, 2, 4 or 8. */
+int bsp_to_sparse(const void* dense, int64_t B, int64_t rows, int64_t cols,
+                  const int64_t* lut, int64_t n, int bs, int elem_bytes,
+                  void* out, void* stream);
+
+/* Compressed -> dense.  Replaces to_dense_forward + to_dense_kernel,
+ * blksprs/ops/conversion.py:463-557, in one pass: block (b, r, c) of the dense
+ * (B, R*bs, C*bs) result is x[packed[b,r,c]] where the reverse LUT entry is
+ * >= 0 and is filled with `fill_bits` (the bit pattern of one element, low
+ * bytes first) elsewhere. */
+int bsp_to_dense(const void* x, int64_t n_x, const int64_t* packed,
+                 int64_t B, int64_t R, int64_t C, int bs, int elem_bytes,
+                 uint64_t fill_bits, void* dense, void* stream);
 
 #ifdef __cplusplus
 }

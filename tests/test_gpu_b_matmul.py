@@ -261,3 +261,18 @@ def test_torch_compile_wrapper_runs():
     out = fn(case["x"].to(DEV), case["lx"].to(DEV), case["y"].to(DEV), case["ly"].to(DEV), case["lo"].to(DEV), 32)
     want = oracle.matmul_forward(case["x"], case["lx"], case["y"], case["ly"], case["lo"], 32)
     assert rel_err(out, want) <= oracle_tolerance(torch.float32)
+
+
+def test_bounded_wait_expires_with_a_status_instead_of_hanging():
+    """Failure detection without a GPU fault: a wait that nothing satisfies runs out after its limit,
+    the kernel returns, the status word says BSP_ERR_DEVICE_TIMEOUT and the context stays usable."""
+    from blksprs_b200 import _cabi
+    lib = _cabi.lib()
+    word = torch.zeros(1, dtype=torch.int32, device=DEV)
+    _cabi.check(lib.bsp_selftest_wait_limit(20000, word.data_ptr(), _cabi.stream_handle(torch.device(DEV))),
+                "bsp_selftest_wait_limit")
+    torch.cuda.synchronize()
+    assert int(word.item()) == _cabi.ERR_DEVICE_TIMEOUT
+    assert lib.bsp_selftest_wait_limit(0, word.data_ptr(), None) == _cabi.ERR_INVALID_ARG
+    # the device still works
+    assert float((torch.ones(4, device=DEV) * 2).sum()) == 8.0
