@@ -16,7 +16,10 @@ template <> struct VecOf<2> { using type = uint16_t; };
 template <> struct VecOf<1> { using type = uint8_t; };
 
 // out[p] = dense[b, r*bs : (r+1)*bs, c*bs : (c+1)*bs] for the p-th LUT row (b, r, c).
-template <int V>
+// A group of GS threads copies one block: a whole CTA for large blocks, one warp for small ones
+// (so that 16 x 16 blocks of 512 bytes still fill the machine).  The writes of a group are
+// contiguous, the reads are bs-element row pieces.
+template <int V, int GS>
 __global__ void __launch_bounds__(256)
 to_sparse_kernel(const unsigned char* __restrict__ dense, int64_t rows, int64_t cols,
                  const int64_t* __restrict__ lut, int64_t n, int bs, int elem_bytes,
@@ -26,45 +29,63 @@ to_sparse_kernel(const unsigned char* __restrict__ dense, int64_t rows, int64_t 
     const int vecs_per_row = (int)(row_bytes / V);
     const int64_t vecs_per_block = (int64_t)bs * vecs_per_row;
     const int64_t pitch = cols * elem_bytes;                   // one dense row
-    for (int64_t p = blockIdx.x; p < n; p += gridDim.x) {
+    const int lane = threadIdx.x % GS;
+    const int64_t groups = (int64_t)gridDim.x * (256 / GS);
+    for (int64_t p = (int64_t)blockIdx.x * (256 / GS) + threadIdx.x / GS; p < n; p += groups) {
         const int64_t b = lut[p * 3 + 0], r = lut[p * 3 + 1], c = lut[p * 3 + 2];
         const unsigned char* src = dense + ((b * rows + r * bs) * cols + c * bs) * elem_bytes;
         unsigned char* dst = out + p * bs * row_bytes;
-        for (int64_t i = threadIdx.x; i < vecs_per_block; i += blockDim.x) {
+        for (int64_t i = lane; i < vecs_per_block; i += GS) {
             const int64_t row = i / vecs_per_row, v = i % vecs_per_row;
-            *reinterpret_cast<Vec*>(dst + row * row_bytes + v * V) =
-                *reinterpret_cast<const Vec*>(src + row * pitch + v * V);
+            *reinterpret_cast<Vec*>(dst + i * V) = *reinterpret_cast<const Vec*>(src + row * pitch + v * V);
         }
     }
 }
 
 // dense[b, r*bs.., c*bs..] = x[packed[b, r, c]] where that is >= 0, else the fill value.
-template <int V>
+// Threads walk the dense result in memory order (whole rows, fully coalesced writes); each
+// vector looks up the block its column range belongs to.  Four vectors per thread are in flight
+// at once; the index arithmetic is 32-bit when the tensor allows it (IDX) and uses shifts for the
+// power-of-two block geometry.
+template <int V, typename IDX>
 __global__ void __launch_bounds__(256)
 to_dense_kernel(const unsigned char* __restrict__ x, int64_t n_x, const int64_t* __restrict__ packed,
                 int64_t n_cells, int64_t R, int64_t C, int bs, int elem_bytes,
                 typename VecOf<V>::type fill, unsigned char* __restrict__ dense) {
     using Vec = typename VecOf<V>::type;
-    const int64_t row_bytes = (int64_t)bs * elem_bytes;
-    const int vecs_per_row = (int)(row_bytes / V);
-    const int64_t vecs_per_block = (int64_t)bs * vecs_per_row;
-    const int64_t pitch = C * row_bytes;
-    for (int64_t cell = blockIdx.x; cell < n_cells; cell += gridDim.x) {
-        const int64_t c = cell % C, br = cell / C;  // br = b * R + r
-        const int64_t src_blk = packed[cell];
-        unsigned char* dst = dense + (br * bs) * pitch + c * row_bytes;
-        if (src_blk >= 0 && src_blk < n_x) {
-            const unsigned char* src = x + src_blk * bs * row_bytes;
-            for (int64_t i = threadIdx.x; i < vecs_per_block; i += blockDim.x) {
-                const int64_t row = i / vecs_per_row, v = i % vecs_per_row;
-                *reinterpret_cast<Vec*>(dst + row * pitch + v * V) =
-                    *reinterpret_cast<const Vec*>(src + row * row_bytes + v * V);
+    constexpr int UNROLL = 4;
+    const int64_t row_bytes = (int64_t)bs * elem_bytes;        // one block row
+    const int vpb_log2 = __ffs((int)(row_bytes / V)) - 1;      // vectors per block row (power of two)
+    const int bs_log2 = __ffs(bs) - 1;
+    const IDX vecs_per_row = (IDX)(C << vpb_log2);             // one dense row
+    const IDX total = (IDX)((n_cells / C) << bs_log2) * vecs_per_row;
+    const IDX stride = (IDX)gridDim.x * blockDim.x;
+    for (IDX g0 = (IDX)blockIdx.x * blockDim.x + threadIdx.x; g0 < total; g0 += stride * UNROLL) {
+        int64_t src_blk[UNROLL];
+        IDX off[UNROLL];
+#pragma unroll
+        for (int k = 0; k < UNROLL; ++k) {
+            const IDX g = g0 + (IDX)k * stride;
+            src_blk[k] = -1;
+            if (g < total) {
+                const IDX drow = g / vecs_per_row, cv = g - drow * vecs_per_row;
+                const IDX c = cv >> vpb_log2, v = cv & (((IDX)1 << vpb_log2) - 1);
+                const IDX br = drow >> bs_log2, row = drow & (IDX)(bs - 1);
+                src_blk[k] = packed[(int64_t)br * C + c];
+                off[k] = (row << vpb_log2) + v;                // vector index inside the block
             }
-        } else {
-            for (int64_t i = threadIdx.x; i < vecs_per_block; i += blockDim.x) {
-                const int64_t row = i / vecs_per_row, v = i % vecs_per_row;
-                *reinterpret_cast<Vec*>(dst + row * pitch + v * V) = fill;
-            }
+        }
+        Vec val[UNROLL];
+#pragma unroll
+        for (int k = 0; k < UNROLL; ++k) {
+            val[k] = fill;
+            if (src_blk[k] >= 0 && src_blk[k] < n_x)
+                val[k] = *reinterpret_cast<const Vec*>(x + (src_blk[k] * bs * row_bytes) + (int64_t)off[k] * V);
+        }
+#pragma unroll
+        for (int k = 0; k < UNROLL; ++k) {
+            const IDX g = g0 + (IDX)k * stride;
+            if (g < total) *reinterpret_cast<Vec*>(dense + (int64_t)g * V) = val[k];
         }
     }
     (void)R;
@@ -77,7 +98,7 @@ static int pick_vector(uintptr_t a, uintptr_t b, int64_t pitch_a, int64_t pitch_
 }
 
 static unsigned copy_grid(int64_t items) {
-    const int64_t cap = 148 * 16;
+    const int64_t cap = 148 * 32;
     return (unsigned)(items < cap ? (items < 1 ? 1 : items) : cap);
 }
 
@@ -105,16 +126,21 @@ extern "C" int bsp_to_sparse(const void* dense, int64_t B, int64_t rows, int64_t
     if (!dense || !lut || !out) return BSP_ERR_INVALID_ARG;
     const int64_t row_bytes = (int64_t)bs * elem_bytes;
     const int v = pick_vector((uintptr_t)dense, (uintptr_t)out, cols * elem_bytes, row_bytes);
-    const unsigned grid = copy_grid(n);
+    const bool big = (int64_t)bs * (row_bytes / v) >= 256;   // vectors per block
+    const unsigned grid = copy_grid(big ? n : (n + 7) / 8);
     auto src = (const unsigned char*)dense;
     auto dst = (unsigned char*)out;
+#define BSP_TO_SPARSE(VV)                                                                                      \
+    if (big) to_sparse_kernel<VV, 256><<<grid, 256, 0, stream>>>(src, rows, cols, lut, n, bs, elem_bytes, dst); \
+    else to_sparse_kernel<VV, 32><<<grid, 256, 0, stream>>>(src, rows, cols, lut, n, bs, elem_bytes, dst)
     switch (v) {
-        case 16: to_sparse_kernel<16><<<grid, 256, 0, stream>>>(src, rows, cols, lut, n, bs, elem_bytes, dst); break;
-        case 8: to_sparse_kernel<8><<<grid, 256, 0, stream>>>(src, rows, cols, lut, n, bs, elem_bytes, dst); break;
-        case 4: to_sparse_kernel<4><<<grid, 256, 0, stream>>>(src, rows, cols, lut, n, bs, elem_bytes, dst); break;
-        case 2: to_sparse_kernel<2><<<grid, 256, 0, stream>>>(src, rows, cols, lut, n, bs, elem_bytes, dst); break;
-        default: to_sparse_kernel<1><<<grid, 256, 0, stream>>>(src, rows, cols, lut, n, bs, elem_bytes, dst); break;
+        case 16: BSP_TO_SPARSE(16); break;
+        case 8: BSP_TO_SPARSE(8); break;
+        case 4: BSP_TO_SPARSE(4); break;
+        case 2: BSP_TO_SPARSE(2); break;
+        default: BSP_TO_SPARSE(1); break;
     }
+#undef BSP_TO_SPARSE
     BSP_LAUNCH_CHECK();
     return BSP_OK;
 }
@@ -130,16 +156,26 @@ extern "C" int bsp_to_dense(const void* x, int64_t n_x, const int64_t* packed, i
     const int64_t row_bytes = (int64_t)bs * elem_bytes;
     int v = pick_vector(n_x > 0 ? (uintptr_t)x : 0, (uintptr_t)dense, row_bytes, C * row_bytes);
     if (v < elem_bytes) v = elem_bytes;  // pointers are at least element aligned
-    const unsigned grid = copy_grid(n_cells);
+    const int64_t total_vecs = B * R * bs * (C * row_bytes / v);
+    const unsigned grid = copy_grid((total_vecs + 1023) / 1024);
     auto src = (const unsigned char*)x;
     auto dst = (unsigned char*)dense;
+    const bool small = total_vecs < 0x7fffffffLL;
+#define BSP_TO_DENSE(VV)                                                                                         \
+    if (small)                                                                                                   \
+        to_dense_kernel<VV, uint32_t><<<grid, 256, 0, stream>>>(src, n_x, packed, n_cells, R, C, bs, elem_bytes,  \
+                                                                make_fill<VV>(fill_bits, elem_bytes), dst);       \
+    else                                                                                                         \
+        to_dense_kernel<VV, int64_t><<<grid, 256, 0, stream>>>(src, n_x, packed, n_cells, R, C, bs, elem_bytes,   \
+                                                               make_fill<VV>(fill_bits, elem_bytes), dst)
     switch (v) {
-        case 16: to_dense_kernel<16><<<grid, 256, 0, stream>>>(src, n_x, packed, n_cells, R, C, bs, elem_bytes, make_fill<16>(fill_bits, elem_bytes), dst); break;
-        case 8: to_dense_kernel<8><<<grid, 256, 0, stream>>>(src, n_x, packed, n_cells, R, C, bs, elem_bytes, make_fill<8>(fill_bits, elem_bytes), dst); break;
-        case 4: to_dense_kernel<4><<<grid, 256, 0, stream>>>(src, n_x, packed, n_cells, R, C, bs, elem_bytes, make_fill<4>(fill_bits, elem_bytes), dst); break;
-        case 2: to_dense_kernel<2><<<grid, 256, 0, stream>>>(src, n_x, packed, n_cells, R, C, bs, elem_bytes, make_fill<2>(fill_bits, elem_bytes), dst); break;
-        default: to_dense_kernel<1><<<grid, 256, 0, stream>>>(src, n_x, packed, n_cells, R, C, bs, elem_bytes, make_fill<1>(fill_bits, elem_bytes), dst); break;
+        case 16: BSP_TO_DENSE(16); break;
+        case 8: BSP_TO_DENSE(8); break;
+        case 4: BSP_TO_DENSE(4); break;
+        case 2: BSP_TO_DENSE(2); break;
+        default: BSP_TO_DENSE(1); break;
     }
+#undef BSP_TO_DENSE
     BSP_LAUNCH_CHECK();
     return BSP_OK;
 }
