@@ -60,6 +60,9 @@ SIGNATURES = {
     "bsp_to_sparse": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "bsp_to_dense": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, ctypes.c_uint64,
                              c_void_p, c_void_p]),
+    "bsp_softmax_fwd": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
+    "bsp_softmax_bwd": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p,
+                                c_void_p]),
     "bsp_selftest_wait_limit": (c_int, [ctypes.c_uint32, c_void_p, c_void_p]),
     "bsp_transpose_blocks": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),
 }

@@ -79,6 +79,13 @@ def validate_dtype_float(*tensors: Tensor) -> None:
             raise ValueError("Tensors must have same dtype")
 
 
+def validate_dtype_float_32(*tensors: Tensor) -> None:
+    if not validation_enabled():
+        return
+    if any(t.dtype != torch.float32 for t in tensors):
+        raise ValueError("Tensor must have float32 dtype")
+
+
 def validate_dtype_supported(*tensors: Tensor) -> None:
     if not validation_enabled():
         return

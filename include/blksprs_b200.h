@@ -297,6 +297,21 @@ int bsp_to_dense(const void* x, int64_t n_x, const int64_t* packed,
                  int64_t B, int64_t R, int64_t C, int bs, int elem_bytes,
                  uint64_t fill_bits, void* dense, void* stream);
 
+/* ---- row-wise block-sparse softmax (fp32) ------------------------------- */
+
+/* out = softmax over every matrix row of the block-sparse tensor, taken over
+ * the row's active blocks only (inactive blocks count as -inf).  Replaces
+ * softmax_forward, blksprs/ops/softmax.py:93-144 (row_wise_max, row_wise_sub,
+ * exp, row_wise_sum, softmax_kernel) and the fused variant :438-466 with one
+ * kernel.  `packed` is the reverse LUT of the (B, R, C) layout. */
+int bsp_softmax_fwd(const float* x, int64_t n_x, const int64_t* packed,
+                    int64_t B, int64_t R, int64_t C, int bs, float* out, void* stream);
+
+/* grad_x = o * (grad_out - sum_row(grad_out * o)).  Replaces softmax_backward,
+ * blksprs/ops/softmax.py:157-208 and :479-520. */
+int bsp_softmax_bwd(const float* grad_out, const float* o, int64_t n_x, const int64_t* packed,
+                    int64_t B, int64_t R, int64_t C, int bs, float* grad_x, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

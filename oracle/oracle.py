@@ -168,6 +168,25 @@ def matmul_backward_via_transpose(grad_out: Tensor, x: Tensor, lx, y: Tensor, ly
     return gx, gy
 
 
+# ---- softmax ------------------------------------------------------------------------
+
+def softmax(x: Tensor, layout, bs: int) -> Tensor:
+    """Row-wise softmax over the active blocks of every row; inactive blocks count as ``-inf``
+    (blksprs/ops/softmax.py:58-61, 93-144), in dense form."""
+    dense = to_dense(x.double(), layout, bs, fill_value=float("-inf"))
+    out = torch.softmax(dense, dim=-1)
+    out = torch.nan_to_num(out, nan=0.0)  # rows without any active block
+    return to_sparse(out, layout, bs).to(x.dtype)
+
+
+def softmax_backward(grad_out: Tensor, out: Tensor, layout, bs: int) -> Tensor:
+    """``o * (g - sum_row(g * o))`` (blksprs/ops/softmax.py:157-208)."""
+    gd = to_dense(grad_out.double(), layout, bs)
+    od = to_dense(out.double(), layout, bs)
+    s = (gd * od).sum(-1, keepdim=True)
+    return to_sparse(od * (gd - s), layout, bs).to(out.dtype)
+
+
 # ---- work model ---------------------------------------------------------------------
 
 def pair_count(lx, ly, lo) -> int:

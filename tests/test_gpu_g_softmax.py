@@ -1,0 +1,98 @@
+"""Block-sparse softmax on the GPU against the CPU oracle and the reference's Triton op, and the attention
+chain matmul -> softmax -> matmul the reference benchmarks (test/cases/test_blocksparse.py:1517-1529)."""
+import os
+import sys
+
+import pytest
+import torch
+
+from gpu_util import DEV, random_layout, rel_err
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("bsz,B,R,C,kept", [(16, 2, 3, 5, 0.6), (32, 3, 4, 4, 0.5), (64, 2, 8, 8, 0.3), (128, 2, 2, 3, 1.0),
+                                             (64, 1, 4, 64, 0.25)])
+def test_forward_and_backward(bsz, B, R, C, kept):
+    import blksprs_b200 as bs
+    g = torch.Generator().manual_seed(bsz + C)
+    layout = random_layout(B, R, C, kept, g)
+    x = torch.randn((int(layout.sum()), bsz, bsz), generator=g) * 3
+    xd = x.to(DEV).requires_grad_(True)
+    out = bs.ops.softmax(xd, layout.to(DEV), bsz)
+    want = oracle.softmax(x, layout, bsz)
+    assert isinstance(out, bs.BlksprsTensor)
+    assert torch.allclose(out.detach().cpu().as_subclass(torch.Tensor), want, atol=1e-6, rtol=1e-5)
+    grad = torch.randn(out.shape, generator=g)
+    out.backward(grad.to(DEV))
+    want_grad = oracle.softmax_backward(grad, want, layout, bsz)
+    assert torch.allclose(xd.grad.cpu(), want_grad, atol=1e-6, rtol=1e-4)
+    for fn in (bs.ops.softmax_regular, bs.ops.softmax_fused):
+        assert torch.equal(fn(x.to(DEV), layout.to(DEV), bsz).as_subclass(torch.Tensor), out.detach().as_subclass(torch.Tensor))
+
+
+def test_rows_sum_to_one_and_errors():
+    import blksprs_b200 as bs
+    bsz = 32
+    layout = torch.tensor([[[1, 0, 1], [0, 0, 1]]], dtype=torch.bool)
+    x = torch.randn((3, bsz, bsz))
+    out = bs.ops.softmax(x.to(DEV), layout.to(DEV), bsz)
+    dense = oracle.to_dense(out.cpu().as_subclass(torch.Tensor), layout, bsz)
+    assert torch.allclose(dense.sum(-1), torch.ones(1, 2 * bsz), atol=1e-5)
+    with pytest.raises(ValueError, match="float32"):
+        bs.ops.softmax(x.to(DEV).half(), layout.to(DEV), bsz)
+    empty = torch.zeros((0, bsz, bsz), device=DEV)
+    assert bs.ops.softmax(empty, torch.zeros((1, 2, 3), dtype=torch.bool, device=DEV), bsz).shape == (0, bsz, bsz)
+
+
+def test_attention_by_parts_matches_dense_attention():
+    """scores = Q K^T on a banded layout, softmax, P V: against dense masked attention."""
+    import blksprs_b200 as bs
+    bsz, B, S, D = 64, 3, 512, 128
+    g = torch.Generator().manual_seed(9)
+    q, k, v = (torch.randn((B, S, D), generator=g) for _ in range(3))
+    n = S // bsz
+    i = torch.arange(n)[:, None]
+    j = torch.arange(n)[None, :]
+    lo = ((j <= i) & ((i - j <= 2) | (j == 0)))[None].expand(B, n, n).contiguous()
+    lq = torch.ones((B, n, D // bsz), dtype=torch.bool)
+    lk = torch.ones((B, D // bsz, n), dtype=torch.bool)
+    dev = lambda t: t.to(DEV)
+    qc = bs.ops.to_sparse(dev(q), dev(lq), bsz)
+    kc = bs.ops.to_sparse(dev(k.transpose(1, 2).contiguous()), dev(lk), bsz)
+    vc = bs.ops.to_sparse(dev(v), dev(lq), bsz)
+    scores = bs.ops.matmul(qc, dev(lq), kc, dev(lk), dev(lo), bsz) * (D ** -0.5)
+    probs = bs.ops.softmax(scores, dev(lo), bsz)
+    out = bs.ops.to_dense(bs.ops.matmul(probs, dev(lo), vc, dev(lq), dev(lq), bsz), dev(lq), bsz)
+    mask = lo.repeat_interleave(bsz, 1).repeat_interleave(bsz, 2)
+    dense_scores = (q @ k.transpose(1, 2)) * (D ** -0.5)
+    want = torch.softmax(dense_scores.masked_fill(~mask, float("-inf")), -1) @ v
+    assert rel_err(out, want) <= 2.5e-3   # two TF32 products and a softmax
+
+
+def test_matches_reference_softmax():
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "blksprs")):
+        pytest.skip("reference package not installed under baseline/_ref")
+    os.environ.setdefault("BLKSPRS_AUTOTUNE", "TEST")
+    sys.path.insert(0, ref_dir)
+    try:
+        import blksprs as ref
+    finally:
+        sys.path.remove(ref_dir)
+    import blksprs_b200 as ours
+    bsz = 32
+    g = torch.Generator().manual_seed(4)
+    layout = random_layout(2, 6, 6, 0.5, g).to(DEV)
+    x = (torch.randn((int(layout.sum()), bsz, bsz), generator=g) * 2).to(DEV)
+    grad = torch.randn(x.shape, generator=g).to(DEV)
+    res = []
+    for lib in (ref, ours):
+        xd = x.clone().requires_grad_(True)
+        out = lib.ops.softmax(xd, layout, bsz)
+        out.backward(grad)
+        res.append((out.detach().as_subclass(torch.Tensor), xd.grad))
+    assert torch.allclose(res[0][0], res[1][0], atol=1e-6, rtol=1e-5)
+    assert torch.allclose(res[0][1], res[1][1], atol=1e-6, rtol=1e-4)
