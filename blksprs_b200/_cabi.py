@@ -63,6 +63,9 @@ SIGNATURES = {
     "bsp_softmax_fwd": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "bsp_softmax_bwd": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p,
                                 c_void_p]),
+    "bsp_bias_add": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p]),
+    "bsp_bias_grad": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p]),
+    "bsp_sum_chunks": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "bsp_selftest_wait_limit": (c_int, [ctypes.c_uint32, c_void_p, c_void_p]),
     "bsp_transpose_blocks": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),
 }

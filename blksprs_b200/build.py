@@ -17,7 +17,8 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 OUT_DIR = PKG_DIR / "lib"
 LIB_PATH = OUT_DIR / "libblksprs_b200.so"
-SOURCES = ["capi.cu", "lut.cu", "plan_panel.cu", "matmul_mma.cu", "matmul_umma.cu", "conversion.cu", "softmax.cu"]
+SOURCES = ["capi.cu", "lut.cu", "plan_panel.cu", "matmul_mma.cu", "matmul_umma.cu", "conversion.cu", "softmax.cu",
+           "linear.cu"]
 HEADERS = [CSRC / "common.cuh", CSRC / "umma_common.cuh", PKG_DIR.parent / "include" / "blksprs_b200.h"]
 
 NVCC_FLAGS = [

@@ -312,6 +312,32 @@ int bsp_softmax_fwd(const float* x, int64_t n_x, const int64_t* packed,
 int bsp_softmax_bwd(const float* grad_out, const float* o, int64_t n_x, const int64_t* packed,
                     int64_t B, int64_t R, int64_t C, int bs, float* grad_x, void* stream);
 
+/* ---- the sparse linear helper (bias and chunked weight gradient) -------- */
+
+/* out[p, r, c] = x[p, r, c] + bias[lut[p][2] * bs + c] for the n_blocks rows
+ * (batch, row, column) of the output LUT `lut` (int64 (n,3)); `bias` holds
+ * n_cols elements of the data dtype.  x and out may be the same buffer.
+ * Replaces the bias branch of apply_torch_linear[_cached],
+ * blksprs/utils/processing.py:72-84 and :170-198 (to_sparse of a repeated
+ * bias slice, `repeat` over the output layout, elementwise add), in one pass
+ * without materialising the bias per block. */
+int bsp_bias_add(const void* x, const int64_t* lut, int64_t n_blocks, int bs,
+                 const void* bias, int64_t n_cols, int dtype, void* out, void* stream);
+
+/* grad_bias[lut[p][2] * bs + c] += sum over r of grad_out[p, r, c], in fp32
+ * (the caller zeroes grad_bias).  Replaces what autograd derives for the same
+ * branch: the backward of the add, of `repeat` and of to_sparse
+ * (blksprs/utils/processing.py:72-84). */
+int bsp_bias_grad(const void* grad_out, const int64_t* lut, int64_t n_blocks, int bs,
+                  int dtype, float* grad_bias, int64_t n_cols, void* stream);
+
+/* out[i] = sum over s < n_chunks of parts[s * numel + i], accumulated in fp32
+ * and rounded once; numel is a multiple of 8.  Folds the per-chunk weight
+ * gradients of the linear helper; the reference gets the same sum from the
+ * backward of `w.repeat(batch, 1, 1)` (blksprs/utils/processing.py:52). */
+int bsp_sum_chunks(const void* parts, int64_t n_chunks, int64_t numel, int dtype,
+                   void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -187,6 +187,37 @@ def softmax_backward(grad_out: Tensor, out: Tensor, layout, bs: int) -> Tensor:
     return to_sparse(od * (gd - s), layout, bs).to(out.dtype)
 
 
+# ---- linear layer on a compressed tensor ---------------------------------------------
+
+def linear(x: Tensor, layout, bs: int, weight: Tensor, bias: Tensor | None = None):
+    """``apply_torch_linear`` in dense form (blksprs/utils/processing.py:26-86): expand ``x`` with
+    zeros, ``x @ weight.T (+ bias)`` in fp32, compress by the output layout — all blocks when a bias
+    is present, else the block rows of ``x`` that hold a block (processing.py:56-64).  This is the
+    check the reference's own test makes against ``torch.nn.Linear``
+    (test/cases/test_blocksparse.py:1158-1184).  Returns (compressed result, output layout)."""
+    a = _as_numpy(layout) != 0
+    B, R, _ = a.shape
+    n_blocks = weight.shape[0] // bs
+    out = to_dense(x.float(), layout, bs) @ weight.float().transpose(-1, -2)
+    if bias is not None:
+        out = out + bias.float()
+        layout_out = np.ones((B, R, n_blocks), dtype=bool)
+    else:
+        layout_out = np.broadcast_to(a.any(-1, keepdims=True), (B, R, n_blocks)).copy()
+    return to_sparse(out, layout_out, bs).to(x.dtype), layout_out
+
+
+def linear_backward(grad_out: Tensor, layout_out, x: Tensor, layout, bs: int, weight: Tensor, has_bias: bool):
+    """Gradients of :func:`linear` in dense form: ``dX = dO @ W`` on x's layout, ``dW = dO^T @ X``
+    summed over batch and rows, ``db = sum(dO)`` (what autograd derives for processing.py:48-84)."""
+    gd = to_dense(grad_out.float(), layout_out, bs)
+    xd = to_dense(x.float(), layout, bs)
+    gx = to_sparse(gd @ weight.float(), layout, bs).to(x.dtype)
+    gw = torch.einsum("brn,brk->nk", gd, xd)
+    gb = gd.sum((0, 1)) if has_bias else None
+    return gx, gw, gb
+
+
 # ---- work model ---------------------------------------------------------------------
 
 def pair_count(lx, ly, lo) -> int:
