@@ -54,7 +54,8 @@ SIGNATURES = {
                                 c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "bsp_panel_fill": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
                                c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
-    "bsp_matmul_umma": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+    "bsp_matmul_umma": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p,
+                                c_void_p, c_int64,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int, c_int, c_int, c_int,
                                 c_void_p, c_void_p]),
     "bsp_to_sparse": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),

@@ -98,10 +98,11 @@ __device__ __forceinline__ uint64_t chunk_desc(uint32_t base, int kk) {
     return make_smem_desc(base + kk * 32, 16, 1024);
 }
 
-template <typename T, int BS, int OP, int G>
+template <typename T, int BS, int OP, int G, bool BIAS>
 __global__ void __launch_bounds__(PCfg<BS, G>::kThreads, PCfg<BS, G>::kCtasPerSm)
 matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    int64_t n_a, int64_t n_b, T* __restrict__ out,
+                   const T* __restrict__ bias, const int64_t* __restrict__ out_lut,
                    const int32_t* __restrict__ panel_first, const int32_t* __restrict__ step_off,
                    const int32_t* __restrict__ steps, const int32_t* __restrict__ touched,
                    const int32_t* __restrict__ unit_panel, const int32_t* __restrict__ unit_step,
@@ -243,6 +244,9 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             // with the step's last chunk
                             ctrl_slot[slot] = (ctrl & (kc == 0 ? ~0u : ~0xF0u)) & (kc == KC - 1 ? ~0u : ~kCtrlLast);
                             armed[slot] = (int)phase;
+#ifdef BSP_EXP_SKIP_A
+                            mbar_arrive_expect_tx(fbar, (__popc(present)) * L::kChunkBytes);
+#else
                             mbar_arrive_expect_tx(fbar, (1 + __popc(present)) * L::kChunkBytes);
                             if (A_MN) {
 #pragma unroll
@@ -251,6 +255,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             } else {
                                 tma_load_2d(sa, &map_a, kc * 64, ia * BS, fbar);
                             }
+#endif
 #pragma unroll
                             for (int q = 0; q < G; ++q) {
                                 if ((present >> q) & 1u) {
@@ -395,10 +400,21 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             bool alive = true;
             PROF_DECL(w_tfull);
             PROF_T0(t_start);
-            auto zero_quarter = [&](T* o) {
+            // the bias row of output block p (nullptr without a bias): bias[column block * BS ...]
+            auto bias_of = [&](int p) -> const T* {
+                if constexpr (!BIAS) return nullptr;
+                return bias + out_lut[(int64_t)p * 3 + 2] * BS;
+            };
+            // a block nothing was accumulated into: zeros, or the bias row repeated
+            auto zero_quarter = [&](T* o, const T* brow) {
                 uint4* dst = reinterpret_cast<uint4*>(o + (int64_t)wq * ROWS_PER_WARP * BS);
-                constexpr int VECS = ROWS_PER_WARP * BS * 2 / 16;
-                for (int i = lane; i < VECS; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
+                constexpr int VECS = ROWS_PER_WARP * BS * 2 / 16, ROW_VECS = BS * 2 / 16;
+                if (BIAS && brow) {
+                    const uint4* bv = reinterpret_cast<const uint4*>(brow);
+                    for (int i = lane; i < VECS; i += 32) dst[i] = __ldg(bv + i % ROW_VECS);
+                } else {
+                    for (int i = lane; i < VECS; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
+                }
             };
             for (int u = blockIdx.x; u < n_units && alive; u += gridDim.x) {
                 const int pn_begin = unit_panel[u], pn_end = unit_panel[u + 1];
@@ -418,7 +434,8 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         const int nsteps = __shfl_sync(0xffffffffu, my_steps, j);
                         const int tmask = __shfl_sync(0xffffffffu, my_touched, j);
                         if (nsteps == 0) {
-                            for (int q = 0; q < g; ++q) zero_quarter(out + (int64_t)(first + q) * BS * BS);
+                            for (int q = 0; q < g; ++q)
+                                zero_quarter(out + (int64_t)(first + q) * BS * BS, bias_of(first + q));
                             continue;
                         }
                         PROF_T0(tw);
@@ -429,8 +446,9 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         tc_fence_after();
                         for (int q = 0; q < g; ++q) {
                             T* o = out + (int64_t)(first + q) * BS * BS;
+                            const T* brow = bias_of(first + q);
                             if (!((tmask >> q) & 1)) {
-                                zero_quarter(o);
+                                zero_quarter(o, brow);
                                 continue;
                             }
                             const uint32_t taddr = tmem_base + grp * (G * BS) + q * BS + ((uint32_t)(wq * 32) << 16);
@@ -439,6 +457,18 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 uint32_t v[32];
                                 tc_ld32(taddr + c0, v);
                                 tc_wait_ld();
+                                if (BIAS && brow) {
+                                    // every lane adds the same 32 bias values (broadcast loads)
+                                    const uint4* bv = reinterpret_cast<const uint4*>(brow + c0);
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) {
+                                        const uint4 b4 = __ldg(bv + i);
+                                        const T* be = reinterpret_cast<const T*>(&b4);
+#pragma unroll
+                                        for (int e = 0; e < 8; ++e)
+                                            v[8 * i + e] = __float_as_uint(__uint_as_float(v[8 * i + e]) + (float)be[e]);
+                                    }
+                                }
                                 if (row_valid) {
                                     // 32 columns = 64 bytes of the row: two 32-byte stores, each a whole sector
                                     T* dst = o + (int64_t)row * BS + c0;
@@ -487,41 +517,45 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
 }
 
-template <typename T, int BS, int OP, int G>
+template <typename T, int BS, int OP, int G, bool BIAS>
 int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_t n_b, void* out,
-               const int32_t* panel_first, const int32_t* step_off, const int32_t* steps,
+               const void* bias, const int64_t* out_lut, const int32_t* panel_first, const int32_t* step_off, const int32_t* steps,
                const int32_t* touched, const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units,
                int dtype, int32_t* status_word, cudaStream_t stream) {
-    auto kern = matmul_umma_kernel<T, BS, OP, G>;
+    auto kern = matmul_umma_kernel<T, BS, OP, G, BIAS>;
     constexpr int smem = PSmem<BS, G>::kTotal;
     BSP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const uint32_t idesc_no_n = make_idesc(dtype, BS, OP) & ~(0x3Fu << 17);
     int ctas = num_sms() * PCfg<BS, G>::kCtasPerSm;
     if (ctas > n_units) ctas = n_units;
-    kern<<<ctas, PCfg<BS, G>::kThreads, smem, stream>>>(ma, mb, n_a, n_b, (T*)out, panel_first, step_off, steps, touched,
+    kern<<<ctas, PCfg<BS, G>::kThreads, smem, stream>>>(ma, mb, n_a, n_b, (T*)out, (const T*)bias, out_lut, panel_first, step_off, steps, touched,
                                            unit_panel, unit_step, n_units, idesc_no_n, status_word);
     BSP_LAUNCH_CHECK();
     return BSP_OK;
 }
 
-#define BSP_LAUNCH_ARGS ma, mb, n_a, n_b, out, panel_first, step_off, steps, touched, unit_panel, unit_step, n_units, dtype, status_word, stream
+#define BSP_LAUNCH_ARGS ma, mb, n_a, n_b, out, bias, out_lut, panel_first, step_off, steps, touched, unit_panel, unit_step, n_units, dtype, status_word, stream
 
 template <typename T, int BS, int G>
 int launch_op(int op, const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_t n_b, void* out,
-              const int32_t* panel_first, const int32_t* step_off, const int32_t* steps, const int32_t* touched,
+              const void* bias, const int64_t* out_lut, const int32_t* panel_first, const int32_t* step_off, const int32_t* steps, const int32_t* touched,
               const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units, int dtype,
               int32_t* status_word, cudaStream_t stream) {
     switch (op) {
-        case BSP_OP_NN: return launch_cfg<T, BS, BSP_OP_NN, G>(BSP_LAUNCH_ARGS);
-        case BSP_OP_NT: return launch_cfg<T, BS, BSP_OP_NT, G>(BSP_LAUNCH_ARGS);
-        case BSP_OP_TN: return launch_cfg<T, BS, BSP_OP_TN, G>(BSP_LAUNCH_ARGS);
+        // a bias is added by the forward product only
+        case BSP_OP_NN:
+            return bias ? launch_cfg<T, BS, BSP_OP_NN, G, true>(BSP_LAUNCH_ARGS)
+                        : launch_cfg<T, BS, BSP_OP_NN, G, false>(BSP_LAUNCH_ARGS);
+        case BSP_OP_NT: return bias ? BSP_ERR_UNSUPPORTED : launch_cfg<T, BS, BSP_OP_NT, G, false>(BSP_LAUNCH_ARGS);
+        case BSP_OP_TN: return bias ? BSP_ERR_UNSUPPORTED : launch_cfg<T, BS, BSP_OP_TN, G, false>(BSP_LAUNCH_ARGS);
         default: return BSP_ERR_INVALID_ARG;
     }
 }
 
 template <typename T>
 int launch_shape(int bs, int width, int op, const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_t n_b,
-                 void* out, const int32_t* panel_first, const int32_t* step_off, const int32_t* steps,
+                 void* out, const void* bias, const int64_t* out_lut, const int32_t* panel_first,
+                 const int32_t* step_off, const int32_t* steps,
                  const int32_t* touched, const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units,
                  int dtype, int32_t* status_word, cudaStream_t stream) {
     if (bs == 64 && width == 1) return launch_op<T, 64, 1>(op, BSP_LAUNCH_ARGS);
@@ -580,7 +614,7 @@ extern "C" int bsp_umma_num_ctas(int dtype, int bs, int width) {
 }
 
 extern "C" int bsp_matmul_umma(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out, int64_t n_out,
-                               const int32_t* panel_first, int64_t n_panels, const int32_t* step_off,
+                               const void* bias, const int64_t* out_lut, const int32_t* panel_first, int64_t n_panels, const int32_t* step_off,
                                const int32_t* steps, const int32_t* touched, const int32_t* unit_panel,
                                const int32_t* unit_step, int32_t n_units, int width, int bs, int dtype, int op,
                                int32_t* status_word, void* stream_) {
@@ -596,6 +630,7 @@ extern "C" int bsp_matmul_umma(const void* a, int64_t n_a, const void* b, int64_
     if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) ||
         (reinterpret_cast<uintptr_t>(out) & 31) || (reinterpret_cast<uintptr_t>(steps) & 15))
         return BSP_ERR_INVALID_ARG;
+    if (bias && (!out_lut || (reinterpret_cast<uintptr_t>(bias) & 15))) return BSP_ERR_INVALID_ARG;
     CUtensorMap ma, mb;
     // a block read MN-major is fetched 64 rows at a time, one read K-major as bs rows x 64 columns
     int st = umma::make_block_map(&ma, a, n_a, bs, dtype, op == BSP_OP_TN ? 64 : bs);

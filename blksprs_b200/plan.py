@@ -221,8 +221,10 @@ def run_pair_plan(plan: PairPlan, a: Tensor, b: Tensor, bs: int) -> Tensor:
     return out
 
 
-def run_step_plan(plan: StepPlan, a: Tensor, b: Tensor, bs: int) -> Tensor:
-    """One block-sparse product with the tcgen05 kernel."""
+def run_step_plan(plan: StepPlan, a: Tensor, b: Tensor, bs: int, bias: Tensor | None = None,
+                  lut_out: Tensor | None = None) -> Tensor:
+    """One block-sparse product with the tcgen05 kernel; ``bias`` (one element per output column, with
+    the output LUT) is added in the kernel's epilogue."""
     device = a.device
     out = torch.empty((plan.n_out, bs, bs), dtype=a.dtype, device=device)
     if plan.n_out == 0:
@@ -230,6 +232,7 @@ def run_step_plan(plan: StepPlan, a: Tensor, b: Tensor, bs: int) -> Tensor:
     with torch.cuda.device(device):
         _cabi.check(_cabi.lib().bsp_matmul_umma(
             _cabi.ptr(a), a.size(0), _cabi.ptr(b), b.size(0), _cabi.ptr(out), plan.n_out,
+            _cabi.ptr(bias), _cabi.ptr(lut_out) if bias is not None else None,
             _cabi.ptr(plan.panel_first), plan.n_panels, _cabi.ptr(plan.step_offsets), _cabi.ptr(plan.steps),
             _cabi.ptr(plan.touched), _cabi.ptr(plan.unit_panel), _cabi.ptr(plan.unit_step), plan.n_units,
             plan.width, bs, _cabi.DATA_DTYPE_CODES[a.dtype], plan.op, _cabi.ptr(status_word(device)),
@@ -271,8 +274,20 @@ class Product:
                 return "umma", 2
         return "umma", 1
 
-    def run(self, a: Tensor, b: Tensor, bs: int) -> Tensor:
+    def run(self, a: Tensor, b: Tensor, bs: int, bias: Tensor | None = None) -> Tensor:
+        """The product; with ``bias`` (data dtype, one element per output column) every output row
+        additionally gets the bias: fused into the tcgen05 kernel's epilogue, a second in-place pass
+        (``bsp_bias_add``) behind the mma.sync kernel."""
         kernel, width = self.choose(bs, a.dtype, a.size(0), b.size(0))
+        if bias is not None and bias.data_ptr() % 16:
+            bias = bias.clone()
         if kernel == "mma":
-            return run_pair_plan(self.pair, a, b, bs)
-        return run_step_plan(self.step_plan(bs, a.dtype, width), a, b, bs)
+            out = run_pair_plan(self.pair, a, b, bs)
+            if bias is not None and out.size(0):
+                with torch.cuda.device(out.device):
+                    _cabi.check(_cabi.lib().bsp_bias_add(
+                        _cabi.ptr(out), _cabi.ptr(self.lut_out), out.size(0), bs, _cabi.ptr(bias), bias.numel(),
+                        _cabi.DATA_DTYPE_CODES[out.dtype], _cabi.ptr(out), _cabi.stream_handle(out.device)),
+                        "bsp_bias_add")
+            return out
+        return run_step_plan(self.step_plan(bs, a.dtype, width), a, b, bs, bias, self.lut_out)

@@ -11,7 +11,8 @@ Same signatures, validation errors, results and gradients as the reference helpe
 * The weight gradient contracts over all ``B*R`` block rows.  To keep every SM busy the rows are
   cut into ``S`` chunks that are multiplied side by side (layouts ``(S, B*R/S, ·)``) and folded in
   fp32 by ``bsp_sum_chunks``; the reference's equivalent is the sum over the batch copies.
-* The bias is added as a vector in one pass (``bsp_bias_add``); its gradient is one column sum
+* The bias stays a vector: the tcgen05 kernel adds it to the accumulators in its epilogue (behind
+  the mma.sync kernel ``bsp_bias_add`` adds it in place); its gradient is one column sum
   (``bsp_bias_grad``).  The reference builds a compressed copy of the bias per output block
   (processing.py:72-84).
 """
@@ -90,17 +91,6 @@ class _LinearPlans:
                               self.K, self.N)
 
 
-def _add_bias(product: Tensor, bias: Tensor, lut_o: Tensor, bs: int) -> Tensor:
-    out = torch.empty_like(product)
-    if product.size(0):
-        with torch.cuda.device(product.device):
-            _cabi.check(_cabi.lib().bsp_bias_add(
-                _cabi.ptr(product), _cabi.ptr(lut_o), product.size(0), bs, _cabi.ptr(bias), bias.numel(),
-                _cabi.DATA_DTYPE_CODES[product.dtype], _cabi.ptr(out), _cabi.stream_handle(product.device)),
-                "bsp_bias_add")
-    return out
-
-
 def _bias_gradient(grad_output: Tensor, lut_o: Tensor, bs: int, n_cols: int) -> Tensor:
     grad = torch.zeros(n_cols, dtype=torch.float32, device=grad_output.device)
     if grad_output.size(0):
@@ -133,10 +123,7 @@ class _SparseLinear(torch.autograd.Function):
         ctx.save_for_backward(x, w_t)
         ctx.plans, ctx.sparsity_block_size = plans, bs
         ctx.bias_cols = None if bias is None else bias.numel()
-        out = plans.forward.run(x, w_t, bs)
-        if bias is not None:
-            out = _add_bias(out, bias, plans.lut_o, bs)
-        return out
+        return plans.forward.run(x, w_t, bs, bias)
 
     @staticmethod
     @torch.autograd.function.once_differentiable

@@ -253,9 +253,16 @@ int bsp_panel_fill(const int64_t* lut_out, const int32_t* panel_first, int64_t n
  *   unit_panel  int32 (n_units+1): the panels split into contiguous units of
  *               about equal cost (bsp_plan_schedule on step_offsets); CTA c of
  *               the launch works on units c, c + n_ctas, ...
- *   unit_step   int32 (n_units+1): step_offsets[unit_panel[u]] */
+ *   unit_step   int32 (n_units+1): step_offsets[unit_panel[u]]
+ *   bias        NULL, or one element of the data dtype per output column
+ *               (16-byte aligned): out[p, r, c] additionally gets
+ *               bias[out_lut[p][2] * bs + c], added to the fp32 accumulator
+ *               before the single rounding — the bias branch of
+ *               apply_torch_linear, blksprs/utils/processing.py:72-84, fused
+ *               into the product's epilogue
+ *   out_lut     the output LUT (int64 (n_out, 3)); read only with a bias */
 int bsp_matmul_umma(const void* a, int64_t n_a, const void* b, int64_t n_b,
-                    void* out, int64_t n_out,
+                    void* out, int64_t n_out, const void* bias, const int64_t* out_lut,
                     const int32_t* panel_first, int64_t n_panels,
                     const int32_t* step_offsets, const int32_t* steps, const int32_t* touched,
                     const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units,
