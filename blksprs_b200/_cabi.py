@@ -56,8 +56,8 @@ SIGNATURES = {
                                c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "bsp_matmul_umma": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p,
                                 c_void_p, c_int64,
-                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int, c_int, c_int, c_int,
-                                c_void_p, c_void_p]),
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_int, c_int, c_int,
+                                c_int, c_void_p, c_void_p]),
     "bsp_to_sparse": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "bsp_to_dense": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, ctypes.c_uint64,
                              c_void_p, c_void_p]),

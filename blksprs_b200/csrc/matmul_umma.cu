@@ -39,6 +39,8 @@ using namespace umma;
 namespace {
 
 constexpr uint32_t kCtrlLast = 0x100u;
+// Slots of the per-CTA queue of unit numbers (dynamic scheduling).
+constexpr int kUnitQueue = 8;
 
 #ifdef BSP_UMMA_PROFILE
 // Debug build only: per-CTA cycle counters (8 per CTA) read back by bsp_debug_read_prof.
@@ -84,7 +86,7 @@ struct PSmem {
     static constexpr int kStageBytes = (1 + G) * kChunkBytes;
     static constexpr int kDataBytes = PCfg<BS, G>::kStages * kStageBytes;
     static constexpr int kBarBytes = (2 * PCfg<BS, G>::kStages + 2 * PCfg<BS, G>::kGroups + 1) * 8;
-    static constexpr int kMiscBytes = (2 * PCfg<BS, G>::kStages + 2) * 4;
+    static constexpr int kMiscBytes = (2 * PCfg<BS, G>::kStages + 2 + kUnitQueue + 5) * 4;
     static constexpr int kTotal = kDataBytes + kBarBytes + kMiscBytes + 1024;
 };
 
@@ -106,7 +108,8 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                    const int32_t* __restrict__ panel_first, const int32_t* __restrict__ step_off,
                    const int32_t* __restrict__ steps, const int32_t* __restrict__ touched,
                    const int32_t* __restrict__ unit_panel, const int32_t* __restrict__ unit_step,
-                   int n_units, uint32_t idesc_no_n, int32_t* __restrict__ status_word) {
+                   int n_units, uint32_t idesc_no_n, int32_t* __restrict__ sched,
+                   int32_t* __restrict__ status_word) {
     using C = PCfg<BS, G>;
     using L = PSmem<BS, G>;
     constexpr int S = C::kStages, NG = C::kGroups, H = BS / 64, KC = BS / 64;
@@ -126,6 +129,10 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     volatile int* armed = reinterpret_cast<volatile int*>(ctrl_slot + S);
     volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(armed + S);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+    volatile int* unit_q = abort_flag + 1;          // unit numbers, slot = position in this CTA's sequence % kUnitQueue
+    volatile int* q_tail = unit_q + kUnitQueue;     // positions published so far
+    volatile int* q_heads = q_tail + 1;             // per epilogue warp: positions retired
+    const bool dyn = sched != nullptr;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -141,6 +148,9 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
         mbar_init(drain_bar, 1);
         *abort_flag = 0;
+        unit_q[0] = (int)blockIdx.x < n_units ? (int)blockIdx.x : -1;
+        *q_tail = 1;
+        for (int i = 0; i < 4; ++i) q_heads[i] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async;" ::: "memory");
     }
@@ -154,22 +164,51 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
 
-    // Work is dealt in units (contiguous panel ranges of about equal cost): this CTA takes units
-    // blockIdx.x, blockIdx.x + gridDim.x, ...  All CTAs therefore sweep the output in step, so the
-    // operand blocks of one batch are used by all SMs at about the same time and stay in L2.
-    // Inside a unit the i-th ring entry uses stage i % S; a stage's barrier parity is its use count.
+    // Work is dealt in units (contiguous panel ranges of about equal cost).  Every CTA starts with
+    // unit blockIdx.x.  Static schedule (sched == nullptr): it goes on with blockIdx.x + gridDim.x,
+    // ...  Dynamic schedule: the CTA's later units come from a global counter (sched[0]), so a CTA
+    // that falls behind (slower path to L2 / HBM, an unlucky run of heavy panels) simply takes fewer
+    // of them.  Either way the units are handed out in order, so all CTAs sweep the output together
+    // and the operand blocks of one batch stay in L2 while they are in use.
+    // The CTA's sequence of units goes through a small queue in shared memory: producer 0 fetches
+    // the next number one unit ahead of its own progress and publishes it; every role reads
+    // position n of the sequence with unit_at(n).  -1 ends the sequence.
+    // The i-th ring entry of the CTA's whole sequence uses stage i % S; a stage's barrier parity is
+    // its use count.
+    auto unit_at = [&](int n, bool block) -> int {  // -2: not published yet (only if !block)
+        if (!dyn) {
+            const long long u = (long long)blockIdx.x + (long long)n * gridDim.x;
+            return u < n_units ? (int)u : -1;
+        }
+        if (*q_tail <= n) {
+            if (!block) return -2;
+            unsigned long long t0 = 0;
+            for (uint32_t spins = 1; *q_tail <= n; ++spins) {
+                if ((spins & 0x3f) == 0) {
+                    if (t0 == 0) t0 = global_timer();
+                    if (*abort_flag || global_timer() - t0 > kWaitLimitNs) {
+                        *abort_flag = 1;
+                        if (status_word) *status_word = BSP_ERR_DEVICE_TIMEOUT;
+                        return -1;
+                    }
+                }
+            }
+        }
+        __threadfence_block();
+        return unit_q[n % kUnitQueue];
+    };
     if ((int)blockIdx.x < n_units) {
         if (warp < S) {
             // ---------------- producers: warp w owns ring stage w ----------------
-            // ring entry = (step, k-chunk); absolute entry index = step * KC + k-chunk.  Inside a unit
-            // producer w fills entries w, w + S, ...; every producer is a warp of its own (one lane
+            // ring entry = (step, k-chunk); absolute entry index = step * KC + k-chunk.  Producer w
+            // fills the entries whose position in the CTA's sequence is w mod S; every producer is a warp of its own (one lane
             // active), so the stages are refilled independently and the copy instructions of
             // different stages issue in parallel.
             if (lane == 0) {
                 const int slot = warp;
                 const int4* recs = reinterpret_cast<const int4*>(steps);
-                auto unit_range = [&](int uu, int& b, int& e) {
-                    if (uu < n_units) {
+                auto range_of = [&](int uu, int& b, int& e) {
+                    if (uu >= 0) {
                         b = unit_step[uu] * KC;
                         e = unit_step[uu + 1] * KC;
                     } else {
@@ -181,97 +220,27 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     r0 = recs[2 * i];
                     r1 = recs[2 * i + 1];
                 };
-                int u = blockIdx.x, ub, ue, nub, nue;
-                unit_range(u, ub, ue);
-                unit_range(u + gridDim.x, nub, nue);
-                int e = ub + slot;
-                int4 c0 = make_int4(0, 0, 0, 0), c1 = c0, n0 = c0, n1 = c0;
-                bool have = false;
-                if (e < ue) {
-                    load_rec(e, c0, c1);
-                    have = true;
-                }
-                uint32_t uses = 0;  // how often this lane's stage has been filled
+                // Producer 0 of a dynamically scheduled CTA also feeds the unit queue.  It draws a
+                // number from the global counter, lets the answer travel while it issues two more
+                // copies, then publishes it; it keeps the queue two positions ahead of its own unit.
+                const bool scheduler = dyn && slot == 0;
+                int m_pub = 1;             // next queue position to publish
+                int pend = 0;              // counter value drawn for it
+                int pend_age = 0;          // copies issued since the draw
+                bool pend_valid = false, closed = false;  // closed: the end marker is published
                 bool alive = true;
-                PROF_DECL(w_empty);
-                PROF_T0(t_start);
-                while (u < n_units && alive) {
-                    if (e >= ue) {  // nothing (left) for this lane in the unit
-                        u += gridDim.x;
-                        ub = nub;
-                        ue = nue;
-                        unit_range(u + gridDim.x, nub, nue);
-                        e = ub + slot;
-                        have = false;
-                        continue;
-                    }
-                    if (!have) load_rec(e, c0, c1);
-                    // fetch this lane's next record now: later in this unit, or its first in the next
-                    const int ne = e + S;
-                    bool nhave = false;
-                    if (ne < ue) {
-                        load_rec(ne, n0, n1);
-                        nhave = true;
-                    } else if (nub + slot < nue) {
-                        load_rec(nub + slot, n0, n1);
-                        nhave = true;
-                    }
-                    const int kc = e % KC;
-                    int ia = c0.x;
-                    int ib[4] = {c0.y, c0.z, c0.w, c1.x};
-                    const uint32_t ctrl = (uint32_t)c1.y;
-                    const uint32_t present = ctrl & 0xFu;
-                    bool bad = ia < 0 || ia >= n_a;
-#pragma unroll
-                    for (int q = 0; q < G; ++q)
-                        if ((present >> q) & 1u) bad |= ib[q] < 0 || ib[q] >= n_b;
-                    if (bad) {
-                        if (status_word) *status_word = BSP_ERR_DEVICE_RANGE;
-                        ia = 0;
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) ib[q] = 0;
-                    }
-                    const uint32_t phase = uses & 1u;
-                    const uint32_t ebar = empty_bar + 8 * slot, fbar = full_bar + 8 * slot;
-                    const uint32_t sa = data + slot * L::kStageBytes;
-                    const uint32_t sb = sa + L::kChunkBytes;
+                auto draw = [&]() {
+                    pend = atomicAdd(sched, 1);
+                    pend_valid = true;
+                    pend_age = 0;
+                };
+                auto publish = [&]() {
+                    // the slot was last used by position m_pub - kUnitQueue: all epilogue warps must be past it
                     unsigned long long t0 = 0;
-                    PROF_T0(tw);
                     for (uint32_t spins = 1;; ++spins) {
-                        if (mbar_try_wait(ebar, phase ^ 1u)) {
-                            PROF_ADD(w_empty, tw);
-                            // first-touch flags count for the step's first chunk only; the panel ends
-                            // with the step's last chunk
-                            ctrl_slot[slot] = (ctrl & (kc == 0 ? ~0u : ~0xF0u)) & (kc == KC - 1 ? ~0u : ~kCtrlLast);
-                            armed[slot] = (int)phase;
-#ifdef BSP_EXP_SKIP_A
-                            mbar_arrive_expect_tx(fbar, (__popc(present)) * L::kChunkBytes);
-#else
-                            mbar_arrive_expect_tx(fbar, (1 + __popc(present)) * L::kChunkBytes);
-                            if (A_MN) {
-#pragma unroll
-                                for (int h = 0; h < H; ++h)
-                                    tma_load_2d(sa + h * 8192, &map_a, h * 64, ia * BS + kc * 64, fbar);
-                            } else {
-                                tma_load_2d(sa, &map_a, kc * 64, ia * BS, fbar);
-                            }
-#endif
-#pragma unroll
-                            for (int q = 0; q < G; ++q) {
-                                if ((present >> q) & 1u) {
-                                    if (B_MN) {
-#pragma unroll
-                                        for (int h = 0; h < H; ++h)
-                                            tma_load_2d(sb + (q * H + h) * 8192, &map_b, h * 64, ib[q] * BS + kc * 64, fbar);
-                                    } else {
-                                        tma_load_2d(sb + q * L::kChunkBytes, &map_b, kc * 64, ib[q] * BS, fbar);
-                                    }
-                                }
-                            }
-                            ++uses;
-                            break;
-                        }
-                        if ((spins & 0xff) == 0) {
+                        const int head = min(min(q_heads[0], q_heads[1]), min(q_heads[2], q_heads[3]));
+                        if (m_pub - head < kUnitQueue) break;
+                        if ((spins & 0x3f) == 0) {
                             if (t0 == 0) t0 = global_timer();
                             if (*abort_flag || global_timer() - t0 > kWaitLimitNs) {
                                 *abort_flag = 1;
@@ -281,18 +250,143 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             }
                         }
                     }
-                    if (ne < ue) {
-                        e = ne;
-                    } else {
-                        u += gridDim.x;
-                        ub = nub;
-                        ue = nue;
-                        unit_range(u + gridDim.x, nub, nue);
-                        e = ub + slot;
+                    const long long v = (long long)gridDim.x + pend;
+                    const int id = (alive && v < n_units) ? (int)v : -1;
+                    if (id < 0) closed = true;
+                    unit_q[m_pub % kUnitQueue] = id;
+                    __threadfence_block();
+                    *q_tail = m_pub + 1;
+                    ++m_pub;
+                    pend_valid = false;
+                };
+                int n = 0;                 // position in this CTA's unit sequence
+                int goff = 0;              // ring entries of the units before this one, mod S
+                // this lane's first entry of a unit whose entries start at ring position `off`
+                auto first_entry = [&](int b, int off) { return b + (slot - off + S) % S; };
+                int u = unit_at(0, true), ub, ue;
+                range_of(u, ub, ue);
+                int nu = -2, nub = 0, nue = 0;  // the next unit once it is known
+                int4 c0 = make_int4(0, 0, 0, 0), c1 = c0, n0 = c0, n1 = c0;
+                bool have = false;         // (c0, c1) is the record of this lane's next entry
+                uint32_t uses = 0;         // how often this lane's stage has been filled
+                PROF_DECL(w_empty);
+                PROF_T0(t_start);
+                while (u >= 0 && alive) {
+                    auto peek_next = [&]() {
+                        if (nu == -2) {
+                            nu = unit_at(n + 1, false);
+                            if (nu != -2) range_of(nu, nub, nue);
+                        }
+                    };
+                    peek_next();
+                    const int ngoff = (goff + (ue - ub)) % S;
+                    for (int e = first_entry(ub, goff); e < ue && alive; e += S) {
+                        if (!have) load_rec(e, c0, c1);
+                        // fetch this lane's next record now: later in this unit, or its first in the next
+                        const int ne = e + S;
+                        bool nhave = false;
+                        if (ne < ue) {
+                            load_rec(ne, n0, n1);
+                            nhave = true;
+                        } else {
+                            peek_next();
+                            if (nu >= 0 && first_entry(nub, ngoff) < nue) {
+                                load_rec(first_entry(nub, ngoff), n0, n1);
+                                nhave = true;
+                            }
+                        }
+                        const int kc = e % KC;
+                        int ia = c0.x;
+                        int ib[4] = {c0.y, c0.z, c0.w, c1.x};
+                        const uint32_t ctrl = (uint32_t)c1.y;
+                        const uint32_t present = ctrl & 0xFu;
+                        bool bad = ia < 0 || ia >= n_a;
+#pragma unroll
+                        for (int q = 0; q < G; ++q)
+                            if ((present >> q) & 1u) bad |= ib[q] < 0 || ib[q] >= n_b;
+                        if (bad) {
+                            if (status_word) *status_word = BSP_ERR_DEVICE_RANGE;
+                            ia = 0;
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) ib[q] = 0;
+                        }
+                        const uint32_t phase = uses & 1u;
+                        const uint32_t ebar = empty_bar + 8 * slot, fbar = full_bar + 8 * slot;
+                        const uint32_t sa = data + slot * L::kStageBytes;
+                        const uint32_t sb = sa + L::kChunkBytes;
+                        unsigned long long t0 = 0;
+                        PROF_T0(tw);
+                        for (uint32_t spins = 1;; ++spins) {
+                            if (mbar_try_wait(ebar, phase ^ 1u)) {
+                                PROF_ADD(w_empty, tw);
+                                // first-touch flags count for the step's first chunk only; the panel ends
+                                // with the step's last chunk
+                                ctrl_slot[slot] = (ctrl & (kc == 0 ? ~0u : ~0xF0u)) & (kc == KC - 1 ? ~0u : ~kCtrlLast);
+                                armed[slot] = (int)phase;
+#ifdef BSP_EXP_SKIP_A
+                                mbar_arrive_expect_tx(fbar, (__popc(present)) * L::kChunkBytes);
+#else
+                                mbar_arrive_expect_tx(fbar, (1 + __popc(present)) * L::kChunkBytes);
+                                if (A_MN) {
+#pragma unroll
+                                    for (int h = 0; h < H; ++h)
+                                        tma_load_2d(sa + h * 8192, &map_a, h * 64, ia * BS + kc * 64, fbar);
+                                } else {
+                                    tma_load_2d(sa, &map_a, kc * 64, ia * BS, fbar);
+                                }
+#endif
+#pragma unroll
+                                for (int q = 0; q < G; ++q) {
+                                    if ((present >> q) & 1u) {
+                                        if (B_MN) {
+#pragma unroll
+                                            for (int h = 0; h < H; ++h)
+                                                tma_load_2d(sb + (q * H + h) * 8192, &map_b, h * 64, ib[q] * BS + kc * 64, fbar);
+                                        } else {
+                                            tma_load_2d(sb + q * L::kChunkBytes, &map_b, kc * 64, ib[q] * BS, fbar);
+                                        }
+                                    }
+                                }
+                                ++uses;
+                                break;
+                            }
+                            if ((spins & 0xff) == 0) {
+                                if (t0 == 0) t0 = global_timer();
+                                if (*abort_flag || global_timer() - t0 > kWaitLimitNs) {
+                                    *abort_flag = 1;
+                                    if (status_word) *status_word = BSP_ERR_DEVICE_TIMEOUT;
+                                    alive = false;
+                                    break;
+                                }
+                            }
+                        }
+                        if (scheduler && !closed) {
+                            if (pend_valid) {
+                                if (++pend_age >= 2) publish();
+                            } else if (m_pub <= n + 2) {
+                                draw();
+                            }
+                        }
+                        have = nhave;
+                        c0 = n0;
+                        c1 = n1;
                     }
-                    have = nhave;
-                    c0 = n0;
-                    c1 = n1;
+                    if (scheduler && !closed && m_pub <= n + 1) {
+                        // the next unit has to be known now
+                        if (!pend_valid) draw();
+                        publish();
+                    }
+                    if (!alive) break;
+                    if (nu == -2) {
+                        nu = unit_at(n + 1, true);
+                        range_of(nu, nub, nue);
+                    }
+                    u = nu;
+                    ub = nub;
+                    ue = nue;
+                    goff = ngoff;
+                    nu = -2;
+                    ++n;
                 }
                 if (slot == 0) {
                     PROF_STORE(0, clock64() - t_start);
@@ -305,7 +399,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             // stage, descriptor and accumulator arithmetic is then warp-uniform (uniform registers)
             // instead of one diverged lane's, which shortens the issue path measurably.
             {
-                int grp = 0;
+                int grp = 0, stage = 0;     // ring stages are used round-robin across unit boundaries
                 uint32_t stage_parity = 0;  // bit s = parity of the next fill of stage s
                 uint32_t grp_phase = 0;
                 bool new_panel = true, alive = true;
@@ -314,12 +408,14 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 PROF_DECL(w_issue);
                 PROF_DECL(w_commit);
                 PROF_T0(t_start);
-                int u = blockIdx.x;
-                int n_entries = (unit_step[u + 1] - unit_step[u]) * KC;
-                while (u < n_units && alive) {
-                    const int nu = u + gridDim.x;
-                    const int next_entries = nu < n_units ? (unit_step[nu + 1] - unit_step[nu]) * KC : 0;
-                    int stage = 0;
+                auto entries_of = [&](int uu) { return uu >= 0 ? (unit_step[uu + 1] - unit_step[uu]) * KC : 0; };
+                int n = 0;  // position in this CTA's unit sequence
+                int u = unit_at(0, true);
+                int n_entries = entries_of(u);
+                while (u >= 0 && alive) {
+                    // the next unit's size is fetched early when its number is already known
+                    int nu = unit_at(n + 1, false);
+                    int next_entries = entries_of(nu);
                     for (int e = 0; e < n_entries; ++e) {
                         if (new_panel) {
                             PROF_T0(tw);
@@ -378,8 +474,14 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         }
                         if (++stage == S) stage = 0;
                     }
+                    if (!alive) break;
+                    if (nu == -2) {
+                        nu = unit_at(n + 1, true);
+                        next_entries = entries_of(nu);
+                    }
                     u = nu;
                     n_entries = next_entries;
+                    ++n;
                 }
                 if (lane == 0) PROF_STORE(2, clock64() - t_start);
                 if (lane == 0) PROF_STORE(3, w_full);
@@ -416,19 +518,46 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     for (int i = lane; i < VECS; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
                 }
             };
-            for (int u = blockIdx.x; u < n_units && alive; u += gridDim.x) {
-                const int pn_begin = unit_panel[u], pn_end = unit_panel[u + 1];
+            // A lane's panel of a batch of 32: (first block, blocks, steps, touched mask).
+            auto load_meta = [&](int pi, int pend) -> int4 {
+                int4 r = make_int4(0, 0, 0, 0);
+                if (pi < pend) {
+                    r.x = panel_first[pi];
+                    r.y = panel_first[pi + 1] - r.x;
+                    r.z = step_off[pi + 1] - step_off[pi];
+                    r.w = touched[pi];
+                }
+                return r;
+            };
+            // The panel range of the next unit and the panel records of its first batch are fetched
+            // while the current unit is being written, so that a unit boundary costs no memory round trip.
+            int n = 0;  // position in this CTA's unit sequence
+            int u = unit_at(0, true);
+            int pn_begin = 0, pn_end = 0;
+            if (u >= 0) {
+                pn_begin = unit_panel[u];
+                pn_end = unit_panel[u + 1];
+            }
+            int4 meta = load_meta(pn_begin + lane, pn_end);
+            bool meta_ok = true;
+            while (u >= 0 && alive) {
+                int nu = unit_at(n + 1, false), npb = 0, npe = 0;
+                if (nu >= 0) {
+                    npb = unit_panel[nu];
+                    npe = unit_panel[nu + 1];
+                }
+                int4 nmeta = make_int4(0, 0, 0, 0);
+                bool nmeta_ok = false;
                 for (int w0 = pn_begin; w0 < pn_end && alive; w0 += 32) {
-                    const int pi = w0 + lane;
-                    int my_first = 0, my_g = 0, my_steps = 0, my_touched = 0;
-                    if (pi < pn_end) {
-                        my_first = panel_first[pi];
-                        my_g = panel_first[pi + 1] - my_first;
-                        my_steps = step_off[pi + 1] - step_off[pi];
-                        my_touched = touched[pi];
-                    }
+                    if (!meta_ok) meta = load_meta(w0 + lane, pn_end);
+                    meta_ok = false;
+                    const int my_first = meta.x, my_g = meta.y, my_steps = meta.z, my_touched = meta.w;
                     const int m = min(32, pn_end - w0);
                     for (int j = 0; j < m && alive; ++j) {
+                        if (j == m - 1 && w0 + 32 >= pn_end && nu >= 0) {  // the unit's last panel
+                            nmeta = load_meta(npb + lane, npe);
+                            nmeta_ok = true;
+                        }
                         const int first = __shfl_sync(0xffffffffu, my_first, j);
                         const int g = __shfl_sync(0xffffffffu, my_g, j);
                         const int nsteps = __shfl_sync(0xffffffffu, my_steps, j);
@@ -490,6 +619,27 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         if (++grp == NG) { grp = 0; grp_phase ^= 1u; }
                     }
                 }
+                // this warp is done with position n: its queue slot may be reused
+                __syncwarp();
+                if (lane == 0) q_heads[wq] = n + 1;
+                if (!alive) break;
+                if (nu == -2) {
+                    nu = unit_at(n + 1, true);
+                    if (nu >= 0) {
+                        npb = unit_panel[nu];
+                        npe = unit_panel[nu + 1];
+                    }
+                }
+                if (nu >= 0 && !nmeta_ok) {
+                    nmeta = load_meta(npb + lane, npe);
+                    nmeta_ok = true;
+                }
+                u = nu;
+                pn_begin = npb;
+                pn_end = npe;
+                meta = nmeta;
+                meta_ok = nmeta_ok;
+                ++n;
             }
             if (warp == S + 1 && lane == 0) PROF_STORE(7, w_tfull);
         }
@@ -515,13 +665,22 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
                      ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
     }
+    // the last CTA to finish puts the scheduling counters back to zero for the next launch
+    if (dyn && threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(sched + 1, 1) == (int)gridDim.x - 1) {
+            sched[0] = 0;
+            sched[1] = 0;
+            __threadfence();
+        }
+    }
 }
 
 template <typename T, int BS, int OP, int G, bool BIAS>
 int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_t n_b, void* out,
                const void* bias, const int64_t* out_lut, const int32_t* panel_first, const int32_t* step_off, const int32_t* steps,
                const int32_t* touched, const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units,
-               int dtype, int32_t* status_word, cudaStream_t stream) {
+               int32_t* sched, int dtype, int32_t* status_word, cudaStream_t stream) {
     auto kern = matmul_umma_kernel<T, BS, OP, G, BIAS>;
     constexpr int smem = PSmem<BS, G>::kTotal;
     BSP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -529,17 +688,17 @@ int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_
     int ctas = num_sms() * PCfg<BS, G>::kCtasPerSm;
     if (ctas > n_units) ctas = n_units;
     kern<<<ctas, PCfg<BS, G>::kThreads, smem, stream>>>(ma, mb, n_a, n_b, (T*)out, (const T*)bias, out_lut, panel_first, step_off, steps, touched,
-                                           unit_panel, unit_step, n_units, idesc_no_n, status_word);
+                                           unit_panel, unit_step, n_units, idesc_no_n, sched, status_word);
     BSP_LAUNCH_CHECK();
     return BSP_OK;
 }
 
-#define BSP_LAUNCH_ARGS ma, mb, n_a, n_b, out, bias, out_lut, panel_first, step_off, steps, touched, unit_panel, unit_step, n_units, dtype, status_word, stream
+#define BSP_LAUNCH_ARGS ma, mb, n_a, n_b, out, bias, out_lut, panel_first, step_off, steps, touched, unit_panel, unit_step, n_units, sched, dtype, status_word, stream
 
 template <typename T, int BS, int G>
 int launch_op(int op, const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_t n_b, void* out,
               const void* bias, const int64_t* out_lut, const int32_t* panel_first, const int32_t* step_off, const int32_t* steps, const int32_t* touched,
-              const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units, int dtype,
+              const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units, int32_t* sched, int dtype,
               int32_t* status_word, cudaStream_t stream) {
     switch (op) {
         // a bias is added by the forward product only
@@ -557,7 +716,7 @@ int launch_shape(int bs, int width, int op, const CUtensorMap& ma, const CUtenso
                  void* out, const void* bias, const int64_t* out_lut, const int32_t* panel_first,
                  const int32_t* step_off, const int32_t* steps,
                  const int32_t* touched, const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units,
-                 int dtype, int32_t* status_word, cudaStream_t stream) {
+                 int32_t* sched, int dtype, int32_t* status_word, cudaStream_t stream) {
     if (bs == 64 && width == 1) return launch_op<T, 64, 1>(op, BSP_LAUNCH_ARGS);
     if (bs == 64 && width == 2) return launch_op<T, 64, 2>(op, BSP_LAUNCH_ARGS);
     if (bs == 128 && width == 1) return launch_op<T, 128, 1>(op, BSP_LAUNCH_ARGS);
@@ -616,8 +775,8 @@ extern "C" int bsp_umma_num_ctas(int dtype, int bs, int width) {
 extern "C" int bsp_matmul_umma(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out, int64_t n_out,
                                const void* bias, const int64_t* out_lut, const int32_t* panel_first, int64_t n_panels, const int32_t* step_off,
                                const int32_t* steps, const int32_t* touched, const int32_t* unit_panel,
-                               const int32_t* unit_step, int32_t n_units, int width, int bs, int dtype, int op,
-                               int32_t* status_word, void* stream_) {
+                               const int32_t* unit_step, int32_t n_units, int32_t* sched, int width, int bs,
+                               int dtype, int op, int32_t* status_word, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     if (n_a < 1 || n_b < 1 || n_out < 0 || n_panels < 0) return BSP_ERR_INVALID_ARG;
     if (!umma_applicable(dtype, bs) || (width != 1 && width != 2)) return BSP_ERR_UNSUPPORTED;

@@ -32,6 +32,15 @@ BLOCK_COST = 1
 # restart at a unit boundary, small enough that concurrently processed units share operands in L2.
 UNIT_COST = int(os.environ.get("BLKSPRS_B200_UNIT_COST", "48"))
 MAX_UNITS_PER_CTA = int(os.environ.get("BLKSPRS_B200_MAX_UNITS", "64"))
+# With the dynamic schedule a unit is the grain of load balancing: small, but large enough that
+# drawing it from the counter stays invisible.  Measured optimum per block size (a pair of 128-blocks
+# is eight times the work of a pair of 64-blocks).
+UNIT_COST_DYNAMIC = {64: 24, 128: 12}
+MAX_UNITS_PER_CTA_DYNAMIC = 1024
+
+# How the persistent CTAs of the tcgen05 kernel get their units: "dynamic" = from a counter, so CTAs
+# that run slower take fewer units; "static" = round-robin.
+SCHEDULE = os.environ.get("BLKSPRS_B200_SCHED", "dynamic")
 
 KERNELS = ("auto", "mma", "umma", "panel")
 _kernel_choice = os.environ.get("BLKSPRS_B200_KERNEL", "auto")
@@ -124,10 +133,11 @@ class StepPlan:
     unit_panel: Tensor
     unit_step: Tensor
     n_units: int
+    sched: Tensor | None = None  # int32[2] scheduling counters (dynamic unit hand-out); the kernel re-zeroes them
 
 
 def build_step_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor, R: int, K: int, C: int,
-                    width: int, n_ctas: int) -> StepPlan:
+                    width: int, n_ctas: int, bs: int = 64) -> StepPlan:
     """Groups the output blocks of every output row into panels of ``width``, lists each panel's
     steps and cuts the panels into units; one device->host read (the total step count)."""
     device = lut_out.device
@@ -171,15 +181,23 @@ def build_step_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor
         # units: every CTA gets the same number of equal-cost units; a unit is several times the
         # heaviest panel, so that indivisible panels cannot unbalance the CTAs
         cost = n_steps + BLOCK_COST * width * n_panels
-        unit_cost = max(UNIT_COST, 4 * (max_panel_steps + BLOCK_COST * width))
-        per_cta = max(1, min(MAX_UNITS_PER_CTA, round(cost / (max(n_ctas, 1) * unit_cost))))
+        heaviest = max_panel_steps + BLOCK_COST * width
+        # static round-robin: a unit is several times the heaviest panel, so that indivisible
+        # panels cannot unbalance the CTAs; dynamic hand-out needs no such margin
+        if SCHEDULE == "dynamic":
+            target = int(os.environ.get("BLKSPRS_B200_UNIT_COST", UNIT_COST_DYNAMIC.get(bs, 24)))
+            unit_cost, cap = max(target, heaviest), MAX_UNITS_PER_CTA_DYNAMIC
+        else:
+            unit_cost, cap = max(UNIT_COST, 4 * heaviest), MAX_UNITS_PER_CTA
+        per_cta = max(1, min(cap, round(cost / (max(n_ctas, 1) * unit_cost))))
         n_units = max(1, n_ctas * per_cta)
         unit_panel = torch.empty(n_units + 1, dtype=torch.int32, device=device)
         _cabi.check(lib.bsp_plan_schedule(_cabi.ptr(offsets), n_panels, BLOCK_COST * width, n_units,
                                           _cabi.ptr(unit_panel), stream), "bsp_plan_schedule")
         unit_step = offsets[unit_panel.long()].contiguous()
+    sched = torch.zeros(2, dtype=torch.int32, device=device) if SCHEDULE == "dynamic" else None
     return StepPlan(op, n_out, n_panels, n_steps, width, panel_first, offsets, steps, touched, unit_panel,
-                    unit_step, n_units)
+                    unit_step, n_units, sched)
 
 
 _status_words: dict[torch.device, Tensor] = {}
@@ -235,7 +253,7 @@ def run_step_plan(plan: StepPlan, a: Tensor, b: Tensor, bs: int, bias: Tensor | 
             _cabi.ptr(bias), _cabi.ptr(lut_out) if bias is not None else None,
             _cabi.ptr(plan.panel_first), plan.n_panels, _cabi.ptr(plan.step_offsets), _cabi.ptr(plan.steps),
             _cabi.ptr(plan.touched), _cabi.ptr(plan.unit_panel), _cabi.ptr(plan.unit_step), plan.n_units,
-            plan.width, bs, _cabi.DATA_DTYPE_CODES[a.dtype], plan.op, _cabi.ptr(status_word(device)),
+            _cabi.ptr(plan.sched), plan.width, bs, _cabi.DATA_DTYPE_CODES[a.dtype], plan.op, _cabi.ptr(status_word(device)),
             _cabi.stream_handle(device)), "bsp_matmul_umma")
     return out
 
@@ -255,7 +273,7 @@ class Product:
         if key not in self._steps:
             n_ctas = _cabi.lib().bsp_umma_num_ctas(_cabi.DATA_DTYPE_CODES[dtype], bs, width)
             self._steps[key] = build_step_plan(self.op, self.lut_out, self.packed_a, self.packed_b, *self.dims,
-                                               width, n_ctas)
+                                               width, n_ctas, bs)
         return self._steps[key]
 
     def choose(self, bs: int, dtype: torch.dtype, n_a: int, n_b: int) -> tuple[str, int]:

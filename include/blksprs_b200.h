@@ -254,6 +254,11 @@ int bsp_panel_fill(const int64_t* lut_out, const int32_t* panel_first, int64_t n
  *               about equal cost (bsp_plan_schedule on step_offsets); CTA c of
  *               the launch works on units c, c + n_ctas, ...
  *   unit_step   int32 (n_units+1): step_offsets[unit_panel[u]]
+ *   sched       NULL: every CTA takes the units c, c + n_ctas, ... (static).
+ *               Otherwise device int32[2], zero before the first launch: after
+ *               its first unit a CTA draws its next units from this counter, so
+ *               slower CTAs take fewer; the kernel leaves both words zero again.
+ *               One launch at a time per `sched` buffer.
  *   bias        NULL, or one element of the data dtype per output column
  *               (16-byte aligned): out[p, r, c] additionally gets
  *               bias[out_lut[p][2] * bs + c], added to the fp32 accumulator
@@ -266,7 +271,8 @@ int bsp_matmul_umma(const void* a, int64_t n_a, const void* b, int64_t n_b,
                     const int32_t* panel_first, int64_t n_panels,
                     const int32_t* step_offsets, const int32_t* steps, const int32_t* touched,
                     const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units,
-                    int width, int bs, int dtype, int op, int32_t* status_word, void* stream);
+                    int32_t* sched, int width, int bs, int dtype, int op,
+                    int32_t* status_word, void* stream);
 
 /* Self test of the bounded device wait (no reference counterpart): launches one
  * thread that waits at most `limit_us` (1..100000) microseconds on a barrier

@@ -51,8 +51,8 @@ def test_argument_errors_are_reported_without_a_device():
     assert lib.bsp_matmul_mma(None, 0, None, 0, None, 0, None, None, 48, 1, 0, None, None) == _cabi.ERR_INVALID_ARG
     assert lib.bsp_matmul_mma(None, 0, None, 0, None, 0, None, None, 64, 7, 0, None, None) == _cabi.ERR_UNSUPPORTED
     assert lib.bsp_matmul_mma(None, 0, None, 0, None, 0, None, None, 64, 1, 0, None, None) == _cabi.OK
-    assert lib.bsp_matmul_umma(None, 1, None, 1, None, 0, None, None, None, 0, None, None, None, None, None, 0, 2, 32,
-                               1, 0, None, None) == _cabi.ERR_UNSUPPORTED
+    assert lib.bsp_matmul_umma(None, 1, None, 1, None, 0, None, None, None, 0, None, None, None, None, None, 0, None,
+                               2, 32, 1, 0, None, None) == _cabi.ERR_UNSUPPORTED
     assert lib.bsp_bias_add(None, None, 0, 24, None, 0, 1, None, None) == _cabi.ERR_INVALID_ARG
     assert lib.bsp_bias_add(None, None, 0, 32, None, 0, 1, None, None) == _cabi.OK
     assert lib.bsp_bias_grad(None, None, -1, 32, 1, None, 0, None) == _cabi.ERR_INVALID_ARG
