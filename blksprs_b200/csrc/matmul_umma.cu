@@ -323,9 +323,6 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 // with the step's last chunk
                                 ctrl_slot[slot] = (ctrl & (kc == 0 ? ~0u : ~0xF0u)) & (kc == KC - 1 ? ~0u : ~kCtrlLast);
                                 armed[slot] = (int)phase;
-#ifdef BSP_EXP_SKIP_A
-                                mbar_arrive_expect_tx(fbar, (__popc(present)) * L::kChunkBytes);
-#else
                                 mbar_arrive_expect_tx(fbar, (1 + __popc(present)) * L::kChunkBytes);
                                 if (A_MN) {
 #pragma unroll
@@ -334,7 +331,6 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 } else {
                                     tma_load_2d(sa, &map_a, kc * 64, ia * BS, fbar);
                                 }
-#endif
 #pragma unroll
                                 for (int q = 0; q < G; ++q) {
                                     if ((present >> q) & 1u) {
