@@ -113,5 +113,29 @@ def ptr(t: torch.Tensor | None) -> int | None:
     return t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_handle(device: torch.device) -> int:
+    """The ``cudaStream_t`` of the calling thread's current stream on ``device``."""
+    if _raw_stream is not None and device.index is not None:
+        return _raw_stream(device.index)
     return torch.cuda.current_stream(device).cuda_stream
+
+
+class _NoGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def device_guard(device: torch.device):
+    """Context that makes ``device`` the current CUDA device; free when it already is."""
+    if device.index is not None and torch.cuda.current_device() == device.index:
+        return _NO_GUARD
+    return torch.cuda.device(device)

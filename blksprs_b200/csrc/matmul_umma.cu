@@ -30,6 +30,8 @@
 // BSP_ERR_DEVICE_TIMEOUT in the status word, all roles leave their loops, outstanding copies
 // and MMAs are drained with bounded waits, tensor memory is freed and the kernel returns.
 #include "common.cuh"
+#include <atomic>
+
 #include "umma_common.cuh"
 
 namespace bsp {
@@ -679,7 +681,15 @@ int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_
                int32_t* sched, int dtype, int32_t* status_word, cudaStream_t stream) {
     auto kern = matmul_umma_kernel<T, BS, OP, G, BIAS>;
     constexpr int smem = PSmem<BS, G>::kTotal;
-    BSP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    // the shared-memory opt-in is a per-device property of this instantiation: set it once per device
+    static std::atomic<uint64_t> opted_in{0};
+    int dev = 0;
+    BSP_CUDA_TRY(cudaGetDevice(&dev));
+    const uint64_t dev_bit = dev >= 0 && dev < 64 ? (1ull << dev) : 0;
+    if (!(opted_in.load(std::memory_order_acquire) & dev_bit)) {
+        BSP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        opted_in.fetch_or(dev_bit, std::memory_order_release);
+    }
     const uint32_t idesc_no_n = make_idesc(dtype, BS, OP) & ~(0x3Fu << 17);
     int ctas = num_sms() * PCfg<BS, G>::kCtasPerSm;
     if (ctas > n_units) ctas = n_units;

@@ -17,7 +17,7 @@ from .. import _cabi
 from ..plan import Product
 from ..utils.blksprs_tensor import BlksprsTensor
 from ..utils.tools import build_layout_indices, build_packed_indices, cast_for_autocast, count_active_blocks, \
-    finalize_layout_cache, prepare_layout_cache
+    finalize_layout_cache, layout_cache_is_current, prepare_layout_cache
 from ..utils.validation import ensure_contiguous, validate_contiguous, validate_device, validate_dimensions, \
     validate_dtype_float, validate_shape, validate_sparsity, validate_sparsity_block_size, \
     validate_sparsity_layout, validation_enabled
@@ -36,6 +36,7 @@ class _MatmulPlans:
         self.layouts = (sl_x, sl_y, sl_o)
         self.n_x: int | None = None
         self.n_y: int | None = None
+        self.layouts_validated = False  # the layout-only checks passed for this cache
         self.forward: Product | None = None
         self.grad_x: Product | None = None
         self.grad_y: Product | None = None
@@ -117,27 +118,29 @@ class _BlockSparseMatmul(torch.autograd.Function):
         return grad_x, grad_y, None, None, None, None
 
 
-@torch.compiler.disable
-def _matmul_eager(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_output, sparsity_block_size,
-                  layout_cache):
-    x, y = ensure_contiguous(x, y)
-    x, y = cast_for_autocast(x, y)
+def _validate_warm(x: Tensor, y: Tensor, plans: _MatmulPlans, sparsity_block_size: int) -> None:
+    """The checks that depend on ``x`` and ``y`` (messages as in the full validation); everything that
+    depends on the layouts alone was checked when this cache was built and the cache key pins the layouts."""
+    validate_dimensions(x, y)
+    validate_contiguous(x, y)
+    validate_dtype_float(x, y)
+    validate_device(x, y, plans.layouts[2])
+    for tensor, layout, n_blocks in ((x, plans.layouts[0], plans.n_x), (y, plans.layouts[1], plans.n_y)):
+        if tensor.device != layout.device:
+            raise ValueError("Tensor and sparsity layout must be on same device")
+        if not (tensor.size(-1) == tensor.size(-2) == sparsity_block_size):
+            raise ValueError("Blocks not conforming to sparsity block size")
+        if tensor.size(0) != n_blocks:
+            raise ValueError("Mismatch between sparsity layout and blocks")
+    validate_sparsity_block_size(sparsity_block_size, x, y)
 
+
+def _validate_cold(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_output, sparsity_block_size) -> None:
     validate_dimensions(x, y)
     validate_contiguous(x, y, sparsity_layout_output)
     validate_dtype_float(x, y)
     validate_device(x, y, sparsity_layout_output)
-
-    # A warm cache already knows how many blocks each layout holds, which saves
-    # the two device reads of the block-count check.
-    counts = None
-    if layout_cache is not None and validation_enabled():
-        probe = prepare_layout_cache(layout_cache, "matmul", sparsity_layout_x, sparsity_layout_y,
-                                     sparsity_layout_output)
-        plans = probe.get(_PLANS)
-        if plans is not None and plans.n_x is not None:
-            counts = (plans.n_x, plans.n_y)
-    validate_sparsity(sparsity_block_size, (x, sparsity_layout_x), (y, sparsity_layout_y), counts=counts)
+    validate_sparsity(sparsity_block_size, (x, sparsity_layout_x), (y, sparsity_layout_y))
     validate_sparsity_layout(sparsity_layout_output)
     if sparsity_layout_x.size(0) != sparsity_layout_y.size(0):
         raise ValueError("Batch dimensions of tensors must match")
@@ -148,16 +151,39 @@ def _matmul_eager(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_ou
                    "Output sparsity layout")
     validate_sparsity_block_size(sparsity_block_size, x, y)
 
-    layout_cache = matmul_build_layout_cache(layout_cache, sparsity_layout_x, sparsity_layout_y,
-                                             sparsity_layout_output)
-    plans = layout_cache[_PLANS]
-    if plans.n_x is None and validation_enabled():
-        # validate_sparsity has just confirmed these against the layouts
-        plans.n_x, plans.n_y = x.size(0), y.size(0)
+
+def _matmul_eager(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_output, sparsity_block_size,
+                  layout_cache):
+    x, y = ensure_contiguous(x, y)
+    x, y = cast_for_autocast(x, y)
+
+    # A warm cache (same layout objects, unchanged) has the plans and already knows that the layouts are
+    # valid and how many blocks each holds: only the checks on x and y remain, without a device read.
+    plans = None
+    if layout_cache_is_current(layout_cache, "matmul", sparsity_layout_x, sparsity_layout_y,
+                               sparsity_layout_output):
+        plans = layout_cache.get(_PLANS)
+    if plans is not None and plans.forward is not None and (plans.layouts_validated or not validation_enabled()):
+        if validation_enabled():
+            _validate_warm(x, y, plans, sparsity_block_size)
+    else:
+        checked = validation_enabled()
+        if checked:
+            _validate_cold(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_output, sparsity_block_size)
+        layout_cache = matmul_build_layout_cache(layout_cache, sparsity_layout_x, sparsity_layout_y,
+                                                 sparsity_layout_output)
+        plans = layout_cache[_PLANS]
+        if checked:
+            # validate_sparsity has just confirmed the block counts against the layouts
+            plans.n_x, plans.n_y = x.size(0), y.size(0)
+            plans.layouts_validated = True
 
     out = _BlockSparseMatmul.apply(x, y, layout_cache["packed_indices_x"], layout_cache["packed_indices_y"],
                                    plans, sparsity_block_size)
     return BlksprsTensor.wrap(out)
+
+
+_matmul_no_compile = torch.compiler.disable(_matmul_eager)
 
 
 @torch.amp.custom_fwd(device_type="cuda")
@@ -182,5 +208,8 @@ def matmul(x: BlksprsTensor, sparsity_layout_x: Tensor,
     Returns:
         BlksprsTensor: The matrix product in compressed form.
     """
-    return _matmul_eager(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_output,
-                         sparsity_block_size, layout_cache)
+    # torch.compile sees an opaque call (graph break, as for the reference's custom op); eager calls skip
+    # the wrapper that enforces it
+    impl = _matmul_no_compile if torch.compiler.is_compiling() else _matmul_eager
+    return impl(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_output, sparsity_block_size,
+                layout_cache)

@@ -138,6 +138,16 @@ class StepPlan:
     n_units: int
     sched: Tensor | None = None  # int32[2] scheduling counters (dynamic unit hand-out); the kernel re-zeroes them
 
+    def launch_args(self) -> tuple:
+        """The plan's own arguments of ``bsp_matmul_umma`` (pointers are stable: the plan holds the tensors)."""
+        args = self.__dict__.get("_launch_args")
+        if args is None:
+            args = (self.panel_first.data_ptr(), self.n_panels, self.step_offsets.data_ptr(), self.steps.data_ptr(),
+                    self.touched.data_ptr(), self.unit_panel.data_ptr(), self.unit_step.data_ptr(), self.n_units,
+                    None if self.sched is None else self.sched.data_ptr(), self.width)
+            self.__dict__["_launch_args"] = args
+        return args
+
 
 def build_step_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor, R: int, K: int, C: int,
                     width: int, n_ctas: int, bs: int = 64) -> StepPlan:
@@ -208,13 +218,15 @@ _status_words: dict[torch.device, Tensor] = {}
 
 def status_word(device: torch.device) -> Tensor:
     """Per-device int32 word the kernels write BSP_ERR_DEVICE_* codes into (never cleared by them)."""
-    device = torch.device(device)
-    if device.index is None:
-        device = torch.device("cuda", torch.cuda.current_device())
     word = _status_words.get(device)
     if word is None:
-        word = torch.zeros(1, dtype=torch.int32, device=device)
-        _status_words[device] = word
+        device = torch.device(device)
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        word = _status_words.get(device)
+        if word is None:
+            word = torch.zeros(1, dtype=torch.int32, device=device)
+            _status_words[device] = word
     return word
 
 
@@ -234,11 +246,13 @@ def run_pair_plan(plan: PairPlan, a: Tensor, b: Tensor, bs: int) -> Tensor:
     out = torch.empty((plan.n_out, bs, bs), dtype=a.dtype, device=device)
     if plan.n_out == 0:
         return out
-    with torch.cuda.device(device):
-        _cabi.check(_cabi.lib().bsp_matmul_mma(
-            _cabi.ptr(a), a.size(0), _cabi.ptr(b), b.size(0), _cabi.ptr(out), plan.n_out,
-            _cabi.ptr(plan.offsets), _cabi.ptr(plan.pairs), bs, _cabi.DATA_DTYPE_CODES[a.dtype], plan.op,
-            _cabi.ptr(status_word(device)), _cabi.stream_handle(device)), "bsp_matmul_mma")
+    with _cabi.device_guard(device):
+        status = _cabi.lib().bsp_matmul_mma(
+            a.data_ptr(), a.size(0), b.data_ptr(), b.size(0), out.data_ptr(), plan.n_out,
+            plan.offsets.data_ptr(), plan.pairs.data_ptr(), bs, _cabi.DATA_DTYPE_CODES[a.dtype], plan.op,
+            status_word(device).data_ptr(), _cabi.stream_handle(device))
+    if status:
+        _cabi.check(status, "bsp_matmul_mma")
     return out
 
 
@@ -250,14 +264,14 @@ def run_step_plan(plan: StepPlan, a: Tensor, b: Tensor, bs: int, bias: Tensor | 
     out = torch.empty((plan.n_out, bs, bs), dtype=a.dtype, device=device)
     if plan.n_out == 0:
         return out
-    with torch.cuda.device(device):
-        _cabi.check(_cabi.lib().bsp_matmul_umma(
-            _cabi.ptr(a), a.size(0), _cabi.ptr(b), b.size(0), _cabi.ptr(out), plan.n_out,
-            _cabi.ptr(bias), _cabi.ptr(lut_out) if bias is not None else None,
-            _cabi.ptr(plan.panel_first), plan.n_panels, _cabi.ptr(plan.step_offsets), _cabi.ptr(plan.steps),
-            _cabi.ptr(plan.touched), _cabi.ptr(plan.unit_panel), _cabi.ptr(plan.unit_step), plan.n_units,
-            _cabi.ptr(plan.sched), plan.width, bs, _cabi.DATA_DTYPE_CODES[a.dtype], plan.op, _cabi.ptr(status_word(device)),
-            _cabi.stream_handle(device)), "bsp_matmul_umma")
+    with _cabi.device_guard(device):
+        status = _cabi.lib().bsp_matmul_umma(
+            a.data_ptr(), a.size(0), b.data_ptr(), b.size(0), out.data_ptr(), plan.n_out,
+            None if bias is None else bias.data_ptr(), None if bias is None else lut_out.data_ptr(),
+            *plan.launch_args(), bs, _cabi.DATA_DTYPE_CODES[a.dtype], plan.op,
+            status_word(device).data_ptr(), _cabi.stream_handle(device))
+    if status:
+        _cabi.check(status, "bsp_matmul_umma")
     return out
 
 

@@ -129,6 +129,33 @@ def _cache_contents_state(layout_cache: LayoutCache) -> tuple:
     return tuple((k, _snapshot(v)) for k, v in sorted(layout_cache.items()) if k not in _BOOKKEEPING)
 
 
+def _cache_key(operation: str, values, held: list | None = None):
+    token = object()
+
+    def key_of(value: object):
+        if isinstance(value, Tensor):
+            if held is not None:
+                held.append(value)
+            return _tensor_identity(value, token)
+        if isinstance(value, (tuple, list, Size)):
+            return tuple(key_of(v) for v in value)
+        if isinstance(value, dict):
+            return tuple(sorted((k, key_of(v)) for k, v in value.items()))
+        return value
+
+    return operation, tuple(key_of(v) for v in values)
+
+
+def layout_cache_is_current(layout_cache: LayoutCache | None, operation: str, *values: object) -> bool:
+    """True if ``layout_cache`` was built by ``operation`` for exactly these inputs and nothing stored in
+    it was replaced or mutated since ``finalize_layout_cache`` (the reuse rule of ``prepare_layout_cache``)."""
+    if not layout_cache:
+        return False
+    recorded = layout_cache.get(_STATE)
+    return (recorded is not None and layout_cache.get(_KEY) == _cache_key(operation, values)
+            and _cache_contents_state(layout_cache) == recorded)
+
+
 def prepare_layout_cache(layout_cache: LayoutCache | None, operation: str, *values: object) -> LayoutCache:
     """Returns a cache dict for ``operation`` that is empty unless it was built for exactly these inputs.
 
@@ -140,19 +167,7 @@ def prepare_layout_cache(layout_cache: LayoutCache | None, operation: str, *valu
     if layout_cache is None:
         layout_cache = {}
     held: list[Tensor] = []
-    token = object()
-
-    def key_of(value: object):
-        if isinstance(value, Tensor):
-            held.append(value)
-            return _tensor_identity(value, token)
-        if isinstance(value, (tuple, list, Size)):
-            return tuple(key_of(v) for v in value)
-        if isinstance(value, dict):
-            return tuple(sorted((k, key_of(v)) for k, v in value.items()))
-        return value
-
-    wanted = (operation, tuple(key_of(v) for v in values))
+    wanted = _cache_key(operation, values, held)
     recorded = layout_cache.get(_STATE)
     fresh = (layout_cache.get(_KEY) != wanted or recorded is None
              or _cache_contents_state(layout_cache) != recorded)
