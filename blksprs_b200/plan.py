@@ -39,7 +39,7 @@ MAX_UNITS_PER_CTA = int(os.environ.get("BLKSPRS_B200_MAX_UNITS", "64"))
 # is what keeps the operand blocks they share in L2 (units that start large and shrink towards the
 # end measured 5-15 % slower than uniform small ones).
 UNIT_COST_DYNAMIC = {64: 24, 128: 12}
-MAX_UNITS_DYNAMIC = 1 << 20
+MAX_UNITS_PER_CTA_DYNAMIC = 1024
 
 # How the persistent CTAs of the tcgen05 kernel get their units: "dynamic" = from a counter, so CTAs
 # that run slower take fewer units; "static" = round-robin.
@@ -136,17 +136,29 @@ class StepPlan:
     unit_panel: Tensor
     unit_step: Tensor
     n_units: int
-    sched: Tensor | None = None  # int32[2] scheduling counters (dynamic unit hand-out); the kernel re-zeroes them
+    dynamic: bool = False  # units are handed out from a counter (else round-robin)
 
     def launch_args(self) -> tuple:
         """The plan's own arguments of ``bsp_matmul_umma`` (pointers are stable: the plan holds the tensors)."""
         args = self.__dict__.get("_launch_args")
         if args is None:
             args = (self.panel_first.data_ptr(), self.n_panels, self.step_offsets.data_ptr(), self.steps.data_ptr(),
-                    self.touched.data_ptr(), self.unit_panel.data_ptr(), self.unit_step.data_ptr(), self.n_units,
-                    None if self.sched is None else self.sched.data_ptr(), self.width)
+                    self.touched.data_ptr(), self.unit_panel.data_ptr(), self.unit_step.data_ptr(), self.n_units)
             self.__dict__["_launch_args"] = args
         return args
+
+    def sched_ptr(self, stream: int) -> int | None:
+        """The scheduling counters (int32[2], zero between launches) of this plan for launches on ``stream``.
+        Launches of one stream run one after the other and may share a pair; every other stream gets its own,
+        so that concurrent launches of one plan never draw from the same counter."""
+        if not self.dynamic:
+            return None
+        table = self.__dict__.setdefault("_sched", {})
+        counters = table.get(stream)
+        if counters is None:
+            counters = torch.zeros(2, dtype=torch.int32, device=self.steps.device)
+            table[stream] = counters
+        return counters.data_ptr()
 
 
 def build_step_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor, R: int, K: int, C: int,
@@ -199,7 +211,9 @@ def build_step_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor
         # panels cannot unbalance the CTAs; dynamic hand-out needs no such margin
         if SCHEDULE == "dynamic":
             target = int(os.environ.get("BLKSPRS_B200_UNIT_COST", UNIT_COST_DYNAMIC.get(bs, 24)))
-            n_units = max(1, min(round(cost / max(target, heaviest)), MAX_UNITS_DYNAMIC))
+            # a whole number of units per CTA: equally fast CTAs then finish together
+            per_cta = max(1, min(MAX_UNITS_PER_CTA_DYNAMIC, round(cost / (max(n_ctas, 1) * max(target, heaviest)))))
+            n_units = max(1, n_ctas * per_cta)
         else:
             unit_cost = max(UNIT_COST, 4 * heaviest)
             per_cta = max(1, min(MAX_UNITS_PER_CTA, round(cost / (max(n_ctas, 1) * unit_cost))))
@@ -208,9 +222,8 @@ def build_step_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor
         _cabi.check(lib.bsp_plan_schedule(_cabi.ptr(offsets), n_panels, BLOCK_COST * width, n_units,
                                           _cabi.ptr(unit_panel), stream), "bsp_plan_schedule")
         unit_step = offsets[unit_panel.long()].contiguous()
-    sched = torch.zeros(2, dtype=torch.int32, device=device) if SCHEDULE == "dynamic" else None
     return StepPlan(op, n_out, n_panels, n_steps, width, panel_first, offsets, steps, touched, unit_panel,
-                    unit_step, n_units, sched)
+                    unit_step, n_units, SCHEDULE == "dynamic")
 
 
 _status_words: dict[torch.device, Tensor] = {}
@@ -265,11 +278,12 @@ def run_step_plan(plan: StepPlan, a: Tensor, b: Tensor, bs: int, bias: Tensor | 
     if plan.n_out == 0:
         return out
     with _cabi.device_guard(device):
+        stream = _cabi.stream_handle(device)
         status = _cabi.lib().bsp_matmul_umma(
             a.data_ptr(), a.size(0), b.data_ptr(), b.size(0), out.data_ptr(), plan.n_out,
             None if bias is None else bias.data_ptr(), None if bias is None else lut_out.data_ptr(),
-            *plan.launch_args(), bs, _cabi.DATA_DTYPE_CODES[a.dtype], plan.op,
-            status_word(device).data_ptr(), _cabi.stream_handle(device))
+            *plan.launch_args(), plan.sched_ptr(stream), plan.width, bs, _cabi.DATA_DTYPE_CODES[a.dtype], plan.op,
+            status_word(device).data_ptr(), stream)
     if status:
         _cabi.check(status, "bsp_matmul_umma")
     return out

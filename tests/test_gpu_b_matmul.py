@@ -263,6 +263,34 @@ def test_torch_compile_wrapper_runs():
     assert rel_err(out, want) <= oracle_tolerance(torch.float32)
 
 
+@pytest.mark.parametrize("schedule", ["dynamic", "static"])
+def test_one_plan_on_two_streams_and_both_schedules(schedule, monkeypatch):
+    """The same layout cache used from two CUDA streams at once (each stream has its own scheduling
+    counters), under the counter-driven and the round-robin hand-out of units."""
+    import blksprs_b200 as bs
+    from blksprs_b200 import plan
+    monkeypatch.setattr(plan, "SCHEDULE", schedule)
+    case = make_case(16, 1024, 1024, 1024, 64, 0.5, torch.bfloat16, seed=31, out_layout="exact")
+    want = oracle.matmul_forward(case["x"], case["lx"], case["y"], case["ly"], case["lo"], 64)
+    lx, ly, lo = (case[k].to(DEV) for k in ("lx", "ly", "lo"))
+    x, y = case["x"].to(DEV), case["y"].to(DEV)
+    cache = {}
+    first = bs.ops.matmul(x, lx, y, ly, lo, 64, cache)
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(DEV), torch.cuda.Stream(DEV)]
+    outs = [[], []]
+    for _ in range(8):
+        for s, acc in zip(streams, outs):
+            with torch.cuda.stream(s):
+                acc.append(bs.ops.matmul(x, lx, y, ly, lo, 64, cache))
+    torch.cuda.synchronize()
+    plan.check_device_status(torch.device(DEV))
+    assert rel_err(first, want) <= oracle_tolerance(torch.bfloat16)
+    for acc in outs:
+        for out in acc:
+            assert torch.equal(out, first)
+
+
 def test_bounded_wait_expires_with_a_status_instead_of_hanging():
     """Failure detection without a GPU fault: a wait that nothing satisfies runs out after its limit,
     the kernel returns, the status word says BSP_ERR_DEVICE_TIMEOUT and the context stays usable."""
