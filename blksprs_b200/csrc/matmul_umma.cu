@@ -23,15 +23,21 @@
 //                 each) per run and entry, releases the stage with tcgen05.commit, and hands a
 //                 finished accumulator group (the G accumulators of a panel, adjacent
 //                 tensor-memory columns) to the epilogue
-//   warps S+1..S+4 epilogue: tcgen05.ld the fp32 accumulators, convert, write the output blocks
-//                 with 32-byte stores; blocks no step touched are written as zeros
+//   warps S+1..S+4 epilogue: tcgen05.ld the fp32 accumulators, add the bias row if there is one,
+//                 convert, write the output blocks with 32-byte stores; blocks no step touched
+//                 are written as zeros (or the bias row)
+//
+// The panels are cut into small units that are handed out in order: a CTA starts with unit
+// blockIdx.x and then draws unit numbers from a global counter (or, without one, takes every
+// gridDim.x-th unit).  Producer 0 draws two units ahead and publishes the numbers through a
+// queue in shared memory, from which all roles of the CTA read the same sequence.
 //
 // Every wait is bounded (about one second): a wait that runs out records
 // BSP_ERR_DEVICE_TIMEOUT in the status word, all roles leave their loops, outstanding copies
 // and MMAs are drained with bounded waits, tensor memory is freed and the kernel returns.
-#include "common.cuh"
 #include <atomic>
 
+#include "common.cuh"
 #include "umma_common.cuh"
 
 namespace bsp {

@@ -12,8 +12,9 @@ Pair plan (``bsp_plan_*``; consumed by the mma.sync kernel, and the yardstick fo
 Step plan (``bsp_panel_*``; consumed by the tcgen05 kernel): output blocks of one output row are
 grouped into panels of ``width`` (1 or 2); a step is one inner index whose A block exists and that
 hits at least one of the panel's B blocks.  ``unit_panel`` / ``unit_step`` cut the panels into
-contiguous units of equal cost that the persistent CTAs take round-robin, so that all SMs work on
-neighbouring output rows (same batch, same operand blocks in L2) at the same time.
+contiguous units of equal cost that the persistent CTAs take in order — drawn from a counter
+(``SCHEDULE = "dynamic"``, small units) or round-robin (``"static"``, larger units) — so that all
+SMs work on neighbouring output rows (same batch, same operand blocks in L2) at the same time.
 """
 from __future__ import annotations
 
