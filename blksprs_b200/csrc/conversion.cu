@@ -43,52 +43,50 @@ to_sparse_kernel(const unsigned char* __restrict__ dense, int64_t rows, int64_t 
 }
 
 // dense[b, r*bs.., c*bs..] = x[packed[b, r, c]] where that is >= 0, else the fill value.
-// Threads walk the dense result in memory order (whole rows, fully coalesced writes); each
-// vector looks up the block its column range belongs to.  Four vectors per thread are in flight
-// at once; the index arithmetic is 32-bit when the tensor allows it (IDX) and uses shifts for the
-// power-of-two block geometry.
-template <int V, typename IDX>
+// The dense result is cut into tiles of 16 rows x 64 vectors (1 KiB of a row with 16-byte vectors).
+// A CTA copies one tile at a time: thread t owns vector column t % 64 and the rows t / 64, +4, +8,
+// +12 of the tile.  The four rows of a thread lie in the same block, so one look-up in the reverse
+// LUT serves four independent loads; the CTA reads 16 consecutive rows (2 KiB with 64-wide bf16
+// blocks) of every block it touches and writes 1 KiB row segments, so both directions reach HBM as
+// kilobyte-sized pieces.  Fill value and blocks are written in the same pass.
+constexpr int kTileRows = 16, kTileVecs = 64;
+
+template <int V>
 __global__ void __launch_bounds__(256)
 to_dense_kernel(const unsigned char* __restrict__ x, int64_t n_x, const int64_t* __restrict__ packed,
-                int64_t n_cells, int64_t R, int64_t C, int bs, int elem_bytes,
+                int64_t n_block_rows, int64_t C, int bs, int elem_bytes,
                 typename VecOf<V>::type fill, unsigned char* __restrict__ dense) {
     using Vec = typename VecOf<V>::type;
-    constexpr int UNROLL = 4;
     const int64_t row_bytes = (int64_t)bs * elem_bytes;        // one block row
     const int vpb_log2 = __ffs((int)(row_bytes / V)) - 1;      // vectors per block row (power of two)
-    const int bs_log2 = __ffs(bs) - 1;
-    const IDX vecs_per_row = (IDX)(C << vpb_log2);             // one dense row
-    const IDX total = (IDX)((n_cells / C) << bs_log2) * vecs_per_row;
-    const IDX stride = (IDX)gridDim.x * blockDim.x;
-    for (IDX g0 = (IDX)blockIdx.x * blockDim.x + threadIdx.x; g0 < total; g0 += stride * UNROLL) {
-        int64_t src_blk[UNROLL];
-        IDX off[UNROLL];
+    const int64_t vecs_per_row = C << vpb_log2;                // one dense row
+    const int64_t tiles_per_row = (vecs_per_row + kTileVecs - 1) / kTileVecs;
+    const int bands_per_block_row = bs / kTileRows;            // bs is a power of two >= 16
+    const int64_t n_tiles = n_block_rows * bands_per_block_row * tiles_per_row;
+    const int tv = threadIdx.x % kTileVecs, rg = threadIdx.x / kTileVecs;
+    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int64_t band = tile / tiles_per_row;             // 16 dense rows
+        const int64_t cv = (tile - band * tiles_per_row) * kTileVecs + tv;
+        if (cv >= vecs_per_row) continue;
+        const int64_t br = band / bands_per_block_row;         // block row (b * R + r)
+        const int row0 = (int)(band - br * bands_per_block_row) * kTileRows + rg;  // row inside the blocks
+        const int64_t c = cv >> vpb_log2;
+        const int v = (int)(cv & (((int64_t)1 << vpb_log2) - 1));
+        const int64_t blk = packed[br * C + c];
+        Vec val[4];
 #pragma unroll
-        for (int k = 0; k < UNROLL; ++k) {
-            const IDX g = g0 + (IDX)k * stride;
-            src_blk[k] = -1;
-            if (g < total) {
-                const IDX drow = g / vecs_per_row, cv = g - drow * vecs_per_row;
-                const IDX c = cv >> vpb_log2, v = cv & (((IDX)1 << vpb_log2) - 1);
-                const IDX br = drow >> bs_log2, row = drow & (IDX)(bs - 1);
-                src_blk[k] = packed[(int64_t)br * C + c];
-                off[k] = (row << vpb_log2) + v;                // vector index inside the block
-            }
-        }
-        Vec val[UNROLL];
+        for (int k = 0; k < 4; ++k) val[k] = fill;
+        if (blk >= 0 && blk < n_x) {
+            const unsigned char* src = x + blk * bs * row_bytes + (int64_t)v * V;
 #pragma unroll
-        for (int k = 0; k < UNROLL; ++k) {
-            val[k] = fill;
-            if (src_blk[k] >= 0 && src_blk[k] < n_x)
-                val[k] = *reinterpret_cast<const Vec*>(x + (src_blk[k] * bs * row_bytes) + (int64_t)off[k] * V);
+            for (int k = 0; k < 4; ++k)
+                val[k] = *reinterpret_cast<const Vec*>(src + (int64_t)(row0 + 4 * k) * row_bytes);
         }
+        unsigned char* dst = dense + ((br * bs + row0) * vecs_per_row + cv) * V;
 #pragma unroll
-        for (int k = 0; k < UNROLL; ++k) {
-            const IDX g = g0 + (IDX)k * stride;
-            if (g < total) *reinterpret_cast<Vec*>(dense + (int64_t)g * V) = val[k];
-        }
+        for (int k = 0; k < 4; ++k)
+            *reinterpret_cast<Vec*>(dst + (int64_t)(4 * k) * vecs_per_row * V) = val[k];
     }
-    (void)R;
 }
 
 static int pick_vector(uintptr_t a, uintptr_t b, int64_t pitch_a, int64_t pitch_b) {
@@ -156,18 +154,13 @@ extern "C" int bsp_to_dense(const void* x, int64_t n_x, const int64_t* packed, i
     const int64_t row_bytes = (int64_t)bs * elem_bytes;
     int v = pick_vector(n_x > 0 ? (uintptr_t)x : 0, (uintptr_t)dense, row_bytes, C * row_bytes);
     if (v < elem_bytes) v = elem_bytes;  // pointers are at least element aligned
-    const int64_t total_vecs = B * R * bs * (C * row_bytes / v);
-    const unsigned grid = copy_grid((total_vecs + 1023) / 1024);
+    const int64_t tiles = B * R * (bs / kTileRows) * ceil_div(C * (row_bytes / v), kTileVecs);
+    const unsigned grid = copy_grid(tiles);
     auto src = (const unsigned char*)x;
     auto dst = (unsigned char*)dense;
-    const bool small = total_vecs < 0x7fffffffLL;
-#define BSP_TO_DENSE(VV)                                                                                         \
-    if (small)                                                                                                   \
-        to_dense_kernel<VV, uint32_t><<<grid, 256, 0, stream>>>(src, n_x, packed, n_cells, R, C, bs, elem_bytes,  \
-                                                                make_fill<VV>(fill_bits, elem_bytes), dst);       \
-    else                                                                                                         \
-        to_dense_kernel<VV, int64_t><<<grid, 256, 0, stream>>>(src, n_x, packed, n_cells, R, C, bs, elem_bytes,   \
-                                                               make_fill<VV>(fill_bits, elem_bytes), dst)
+#define BSP_TO_DENSE(VV)                                                                          \
+    to_dense_kernel<VV><<<grid, 256, 0, stream>>>(src, n_x, packed, B * R, C, bs, elem_bytes,      \
+                                                  make_fill<VV>(fill_bits, elem_bytes), dst)
     switch (v) {
         case 16: BSP_TO_DENSE(16); break;
         case 8: BSP_TO_DENSE(8); break;
