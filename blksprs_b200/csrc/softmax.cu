@@ -111,6 +111,9 @@ softmax_bwd_kernel(const float* __restrict__ g, const float* __restrict__ o, int
 
 // ---- list-based kernels --------------------------------------------------------------------
 
+// exp through ex2.approx, as the reference's Triton kernels compute it (tl.exp, blksprs/ops/softmax.py:120).
+__device__ inline float fast_exp(float v) { return __expf(v); }
+
 constexpr int kListMax = 8192;  // block columns a CTA can list (32 KiB of shared memory)
 
 // Compacts the active blocks of one block row into list[0..n) (column order), by warp 0.
@@ -160,7 +163,7 @@ softmax_fwd_list_kernel(const float* __restrict__ x, int64_t n_x, const int64_t*
             float s = 0.f;
             for (int idx = lane; idx < total; idx += 32) {
                 const float4 v = *reinterpret_cast<const float4*>(x + piece_offset(list, idx, vpr_log2, row, bs));
-                s += (expf(v.x - m) + expf(v.y - m)) + (expf(v.z - m) + expf(v.w - m));
+                s += (fast_exp(v.x - m) + fast_exp(v.y - m)) + (fast_exp(v.z - m) + fast_exp(v.w - m));
             }
             s = warp_sum(s);
             const float inv = 1.f / s;
@@ -168,10 +171,10 @@ softmax_fwd_list_kernel(const float* __restrict__ x, int64_t n_x, const int64_t*
                 const int64_t off = piece_offset(list, idx, vpr_log2, row, bs);
                 const float4 v = *reinterpret_cast<const float4*>(x + off);
                 float4 o;
-                o.x = expf(v.x - m) * inv;
-                o.y = expf(v.y - m) * inv;
-                o.z = expf(v.z - m) * inv;
-                o.w = expf(v.w - m) * inv;
+                o.x = fast_exp(v.x - m) * inv;
+                o.y = fast_exp(v.y - m) * inv;
+                o.z = fast_exp(v.z - m) * inv;
+                o.w = fast_exp(v.w - m) * inv;
                 *reinterpret_cast<float4*>(out + off) = o;
             }
         }

@@ -1,0 +1,88 @@
+"""Small timing probes of the data-movement kernels around the matmul (conversion, softmax).
+
+``python -m blksprs_b200.perf_probe softmax|conversion [--small]`` prints one line per case with the
+achieved bandwidth (algorithmic bytes / CUDA-event time).  ``--small`` runs one case of a few hundred
+MB, the size used for profiler captures.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+import blksprs_b200 as bs
+
+
+def _time(fn, iters: int) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def softmax(small: bool, iters: int) -> None:
+    cases = [(32, 64, 64, 64, 0.25)] if small else [(128, 64, 64, 64, 0.25), (64, 64, 64, 64, 1.0),
+                                                     (32, 32, 32, 128, 0.5), (256, 64, 64, 16, 0.25)]
+    bs.utils.disable_validation()  # the checks read counts back from the device, which would serialise the launches
+    for B, R, C, bsz, kept in cases:
+        g = torch.Generator().manual_seed(1)
+        layout = torch.rand((B, R, C), generator=g) < kept
+        layout[:, :, 0] = True
+        layout = layout.cuda()
+        n = int(layout.sum())
+        x = torch.randn((n, bsz, bsz), device="cuda")
+        cache = {}
+        xs = x.clone().requires_grad_(True)
+        out = bs.ops.softmax(xs, layout, bsz, layout_cache=cache)
+        grad = torch.randn_like(out)
+
+        def backward():
+            xs.grad = None
+            out.backward(grad, retain_graph=True)
+
+        fwd = _time(lambda: bs.ops.softmax(x, layout, bsz, layout_cache=cache), iters)
+        bwd = _time(backward, iters)
+        nbytes = n * bsz * bsz * 4
+        print(f"softmax B={B} R={R} C={C} bs={bsz} kept={kept}: {nbytes / 2**20:.0f} MiB  "
+              f"forward {fwd * 1e3:.0f} us = {2 * nbytes / fwd / 1e6:.0f} GB/s  "
+              f"backward {bwd * 1e3:.0f} us = {3 * nbytes / bwd / 1e6:.0f} GB/s")
+    bs.utils.enable_validation()
+
+
+def conversion(small: bool, iters: int) -> None:
+    cases = [(64, 8, 4096, 0.25)] if small else [(64, 32, 4096, 0.25), (64, 32, 4096, 1.0), (128, 32, 4096, 0.25),
+                                                  (16, 8, 4096, 0.5)]
+    bs.utils.disable_validation()  # the checks read counts back from the device, which would serialise the launches
+    for bsz, B, n, kept in cases:
+        g = torch.Generator(device="cuda")
+        g.manual_seed(0)
+        layout = torch.rand((B, n // bsz, n // bsz), generator=g, device="cuda") < kept
+        dense = torch.randn((B, n, n), device="cuda", dtype=torch.bfloat16)
+        c1, c2 = {}, {}
+        comp = bs.ops.to_sparse(dense, layout, bsz, c1)
+        for name, fn, nbytes in (
+                ("to_sparse", lambda: bs.ops.to_sparse(dense, layout, bsz, c1), 2 * comp.numel() * 2),
+                ("to_dense", lambda: bs.ops.to_dense(comp, layout, bsz, 0, c2), comp.numel() * 2 + dense.numel() * 2)):
+            ms = _time(fn, iters)
+            print(f"{name} bs={bsz} B={B} n={n} kept={kept}: {ms * 1e3:.0f} us  {nbytes / ms / 1e6:.0f} GB/s "
+                  f"({nbytes / 1e6:.0f} MB moved)")
+    bs.utils.enable_validation()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["softmax", "conversion"])
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    {"softmax": softmax, "conversion": conversion}[args.what](args.small, args.iters)
+
+
+if __name__ == "__main__":
+    main()
