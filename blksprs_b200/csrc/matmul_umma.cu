@@ -144,6 +144,12 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    // Programmatic dependent launch: a following launch of this kernel may move its CTAs onto the
+    // SMs as ours leave and run its set-up (barriers, tensor-memory allocation) meanwhile; it
+    // does not touch global memory before its own griddepcontrol.wait below, which returns when
+    // this grid has completed.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(full_bar + 8 * s, 1);
@@ -171,6 +177,8 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
+    // everything the previous kernels of the stream wrote is visible after this
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // Work is dealt in units (contiguous panel ranges of about equal cost).  Every CTA starts with
     // unit blockIdx.x.  Static schedule (sched == nullptr): it goes on with blockIdx.x + gridDim.x,
@@ -699,9 +707,18 @@ int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_
     const uint32_t idesc_no_n = make_idesc(dtype, BS, OP) & ~(0x3Fu << 17);
     int ctas = num_sms() * PCfg<BS, G>::kCtasPerSm;
     if (ctas > n_units) ctas = n_units;
-    kern<<<ctas, PCfg<BS, G>::kThreads, smem, stream>>>(ma, mb, n_a, n_b, (T*)out, (const T*)bias, out_lut, panel_first, step_off, steps, touched,
-                                           unit_panel, unit_step, n_units, idesc_no_n, sched, status_word);
-    BSP_LAUNCH_CHECK();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3((unsigned)PCfg<BS, G>::kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see griddepcontrol in the kernel
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BSP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, n_a, n_b, (T*)out, (const T*)bias, out_lut, panel_first, step_off,
+                                    steps, touched, unit_panel, unit_step, (int)n_units, idesc_no_n, sched, status_word));
     return BSP_OK;
 }
 
