@@ -1,5 +1,5 @@
 // Block-sparse matmul on 5th-generation tensor cores (tcgen05.mma, accumulators in tensor
-// memory) for fp16 / bf16 data and block sizes 64 and 128.
+// memory) for fp16 / bf16 / fp32 (as TF32) data and block sizes 64 and 128.
 //
 // The work list is a step plan (plan_panel.cu): the output blocks of one output row are grouped
 // into panels of G (1 or 2) blocks; a step is one inner index t whose A block exists and that
@@ -8,10 +8,11 @@
 // of present columns is multiplied by ONE tcgen05.mma of N = run x bs, and the A block is fetched
 // once per step instead of once per (A, B) pair.  With G = 1 a step is a single (A, B) pair.
 //
-// A ring entry is one (step, k-chunk): 64 of the bs contraction indices of the step's blocks,
-// so that for bs = 128 the MMAs of the first half can start while the second half is in flight.
-// A block read K-major contributes its 64-column half k (bs rows x 128 B); a block read
-// MN-major contributes rows [64k, 64k+64) as bs/64 sub-tiles of 64 rows x 128 B.  The
+// A ring entry is one (step, k-chunk): KE = 64 (16-bit data) or 32 (fp32) of the bs contraction
+// indices of the step's blocks, 128 bytes of a K-major row, so that the MMAs of the first chunk can
+// start while the next is in flight.  A block read K-major contributes its KE-column piece k
+// (bs rows x 128 B); a block read MN-major contributes rows [KE k, KE k + KE) as bs/KE sub-tiles of
+// KE rows x 128 B.  The
 // transposed products of the backward pass (BSP_OP_NT, BSP_OP_TN) use the same staged data;
 // only the major-ness bits of the shared-memory and instruction descriptors change.
 //
@@ -102,10 +103,24 @@ struct PSmem {
 // apart).  K-major: rows are M/N indices, 16 contraction elements = 32 bytes along the row.
 // MN-major: rows are contraction indices (16 rows = 2048 B per MMA), the M/N extent is cut
 // into 64-wide atoms of 64 rows x 128 B = 8 KiB, `LBO` apart.
-template <int BS, bool MN_MAJOR>
+// fp32 operands (TF32): an MMA takes 8 contraction elements = again 32 bytes K-major; MN-major it
+// takes 8 rows = 1024 B, the atoms are 32 rows x 128 B = 4 KiB with 4-row groups 512 B apart and
+// the swizzle works on 32-byte granules (layout type 1).
+template <typename T, bool MN_MAJOR>
 __device__ __forceinline__ uint64_t chunk_desc(uint32_t base, int kk) {
-    if (MN_MAJOR) return make_smem_desc(base + kk * 2048, 8192, 1024);
+    if (MN_MAJOR) {
+        if (sizeof(T) == 4) return make_smem_desc(base + kk * 1024, 4096, 512, 1);
+        return make_smem_desc(base + kk * 2048, 8192, 1024);
+    }
     return make_smem_desc(base + kk * 32, 16, 1024);
+}
+
+// One MMA of the element type's kind, issued by the elected lane of a converged warp.
+template <typename T>
+__device__ __forceinline__ void tc_mma_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    if (sizeof(T) == 4) tc_mma_tf32_elect(d_tmem, adesc, bdesc, idesc, accumulate);
+    else tc_mma_f16_elect(d_tmem, adesc, bdesc, idesc, accumulate);
 }
 
 template <typename T, int BS, int OP, int G, bool BIAS>
@@ -120,7 +135,10 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                    int32_t* __restrict__ status_word) {
     using C = PCfg<BS, G>;
     using L = PSmem<BS, G>;
-    constexpr int S = C::kStages, NG = C::kGroups, H = BS / 64, KC = BS / 64;
+    // A ring entry holds KE contraction indices (128 bytes of a K-major row): 64 for 16-bit data, 32 for
+    // fp32; a block read MN-major is staged as BS / KE atoms of KE rows x 128 bytes.
+    constexpr int KE = 128 / (int)sizeof(T), ATOM = KE * 128;
+    constexpr int S = C::kStages, NG = C::kGroups, H = BS / KE, KC = BS / KE;
     constexpr bool A_MN = (OP == BSP_OP_TN);
     constexpr bool B_MN = (OP != BSP_OP_NT);
     constexpr int TMEM_COLS = tmem_cols_pow2(NG * G * BS);
@@ -343,9 +361,9 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 if (A_MN) {
 #pragma unroll
                                     for (int h = 0; h < H; ++h)
-                                        tma_load_2d(sa + h * 8192, &map_a, h * 64, ia * BS + kc * 64, fbar);
+                                        tma_load_2d(sa + h * ATOM, &map_a, h * KE, ia * BS + kc * KE, fbar);
                                 } else {
-                                    tma_load_2d(sa, &map_a, kc * 64, ia * BS, fbar);
+                                    tma_load_2d(sa, &map_a, kc * KE, ia * BS, fbar);
                                 }
 #pragma unroll
                                 for (int q = 0; q < G; ++q) {
@@ -353,9 +371,9 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                         if (B_MN) {
 #pragma unroll
                                             for (int h = 0; h < H; ++h)
-                                                tma_load_2d(sb + (q * H + h) * 8192, &map_b, h * 64, ib[q] * BS + kc * 64, fbar);
+                                                tma_load_2d(sb + (q * H + h) * ATOM, &map_b, h * KE, ib[q] * BS + kc * KE, fbar);
                                         } else {
-                                            tma_load_2d(sb + q * L::kChunkBytes, &map_b, kc * 64, ib[q] * BS, fbar);
+                                            tma_load_2d(sb + q * L::kChunkBytes, &map_b, kc * KE, ib[q] * BS, fbar);
                                         }
                                     }
                                 }
@@ -450,7 +468,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             const uint32_t idesc = idesc_no_n | ((uint32_t)(BS >> 3) << 17);
 #pragma unroll
                             for (int kk = 0; kk < 4; ++kk) {
-                                tc_mma_f16_elect(d0, chunk_desc<BS, A_MN>(sa, kk), chunk_desc<BS, B_MN>(sb, kk), idesc,
+                                tc_mma_elect<T>(d0, chunk_desc<T, A_MN>(sa, kk), chunk_desc<T, B_MN>(sb, kk), idesc,
                                                  ((first & 1u) && kk == 0) ? 0u : 1u);
                             }
                         } else {
@@ -466,11 +484,11 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 const uint32_t idesc = idesc_no_n | ((n >> 3) << 17);
                                 // the run's first B sub-tile: K-major blocks follow each other row after
                                 // row, MN-major blocks are bs/64 atoms of 8 KiB each
-                                const uint32_t sbq = sb + (B_MN ? q0 * H * 8192 : q0 * L::kChunkBytes);
+                                const uint32_t sbq = sb + (B_MN ? q0 * H * ATOM : q0 * L::kChunkBytes);
 #pragma unroll
                                 for (int kk = 0; kk < 4; ++kk) {
-                                    tc_mma_f16_elect(d0 + q0 * BS, chunk_desc<BS, A_MN>(sa, kk),
-                                                     chunk_desc<BS, B_MN>(sbq, kk), idesc, (f && kk == 0) ? 0u : 1u);
+                                    tc_mma_elect<T>(d0 + q0 * BS, chunk_desc<T, A_MN>(sa, kk),
+                                                    chunk_desc<T, B_MN>(sbq, kk), idesc, (f && kk == 0) ? 0u : 1u);
                                 }
                             }
                         }
@@ -522,7 +540,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             // a block nothing was accumulated into: zeros, or the bias row repeated
             auto zero_quarter = [&](T* o, const T* brow) {
                 uint4* dst = reinterpret_cast<uint4*>(o + (int64_t)wq * ROWS_PER_WARP * BS);
-                constexpr int VECS = ROWS_PER_WARP * BS * 2 / 16, ROW_VECS = BS * 2 / 16;
+                constexpr int VECS = ROWS_PER_WARP * BS * (int)sizeof(T) / 16, ROW_VECS = BS * (int)sizeof(T) / 16;
                 if (BIAS && brow) {
                     const uint4* bv = reinterpret_cast<const uint4*>(brow);
                     for (int i = lane; i < VECS; i += 32) dst[i] = __ldg(bv + i % ROW_VECS);
@@ -600,27 +618,41 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 tc_wait_ld();
                                 if (BIAS && brow) {
                                     // every lane adds the same 32 bias values (broadcast loads)
+                                    constexpr int EPV = 16 / (int)sizeof(T);  // elements per 16-byte load
                                     const uint4* bv = reinterpret_cast<const uint4*>(brow + c0);
 #pragma unroll
-                                    for (int i = 0; i < 4; ++i) {
+                                    for (int i = 0; i < 32 / EPV; ++i) {
                                         const uint4 b4 = __ldg(bv + i);
                                         const T* be = reinterpret_cast<const T*>(&b4);
 #pragma unroll
-                                        for (int e = 0; e < 8; ++e)
-                                            v[8 * i + e] = __float_as_uint(__uint_as_float(v[8 * i + e]) + (float)be[e]);
+                                        for (int e = 0; e < EPV; ++e)
+                                            v[EPV * i + e] = __float_as_uint(__uint_as_float(v[EPV * i + e]) + (float)be[e]);
                                     }
                                 }
                                 if (row_valid) {
-                                    // 32 columns = 64 bytes of the row: two 32-byte stores, each a whole sector
                                     T* dst = o + (int64_t)row * BS + c0;
+                                    if constexpr (sizeof(T) == 4) {
+                                        // 32 fp32 columns = 128 bytes of the row: four 32-byte stores
 #pragma unroll
-                                    for (int i = 0; i < 2; ++i) {
-                                        uint32_t w8[8];
+                                        for (int i = 0; i < 4; ++i) {
+                                            uint32_t w8[8];
 #pragma unroll
-                                        for (int e = 0; e < 8; ++e)
-                                            w8[e] = pack2<T>(__uint_as_float(v[16 * i + 2 * e]),
-                                                             __uint_as_float(v[16 * i + 2 * e + 1]));
-                                        st_global_32B(dst + 16 * i, w8);
+                                            for (int e = 0; e < 8; ++e)  // + 0: the vector store gets registers of its
+                                                // own (it cannot take the load's octet in place); -0 becomes +0
+                                                w8[e] = __float_as_uint(__uint_as_float(v[8 * i + e]) + 0.0f);
+                                            st_global_32B(dst + 8 * i, w8);
+                                        }
+                                    } else {
+                                        // 32 columns = 64 bytes of the row: two 32-byte stores, each a whole sector
+#pragma unroll
+                                        for (int i = 0; i < 2; ++i) {
+                                            uint32_t w8[8];
+#pragma unroll
+                                            for (int e = 0; e < 8; ++e)
+                                                w8[e] = pack2<T>(__uint_as_float(v[16 * i + 2 * e]),
+                                                                 __uint_as_float(v[16 * i + 2 * e + 1]));
+                                            st_global_32B(dst + 16 * i, w8);
+                                        }
                                     }
                                 }
                             }
@@ -776,7 +808,7 @@ extern "C" int bsp_debug_read_prof(long long* host_out, int n) {
 #endif
 
 bool umma_applicable(int dtype, int bs) {
-    return (dtype == BSP_F16 || dtype == BSP_BF16) && (bs == 64 || bs == 128);
+    return (dtype == BSP_F16 || dtype == BSP_BF16 || dtype == BSP_F32) && (bs == 64 || bs == 128);
 }
 
 }  // namespace bsp
@@ -821,10 +853,11 @@ extern "C" int bsp_matmul_umma(const void* a, int64_t n_a, const void* b, int64_
     if (bias && (!out_lut || (reinterpret_cast<uintptr_t>(bias) & 15))) return BSP_ERR_INVALID_ARG;
     CUtensorMap ma, mb;
     // a block read MN-major is fetched 64 rows at a time, one read K-major as bs rows x 64 columns
-    int st = umma::make_block_map(&ma, a, n_a, bs, dtype, op == BSP_OP_TN ? 64 : bs);
+    int st = umma::make_block_map(&ma, a, n_a, bs, dtype, op == BSP_OP_TN);
     if (st != BSP_OK) return st;
-    st = umma::make_block_map(&mb, b, n_b, bs, dtype, op != BSP_OP_NT ? 64 : bs);
+    st = umma::make_block_map(&mb, b, n_b, bs, dtype, op != BSP_OP_NT);
     if (st != BSP_OK) return st;
+    if (dtype == BSP_F32) return launch_shape<float>(bs, width, op, BSP_LAUNCH_ARGS);
     if (dtype == BSP_F16) return launch_shape<__half>(bs, width, op, BSP_LAUNCH_ARGS);
     return launch_shape<__nv_bfloat16>(bs, width, op, BSP_LAUNCH_ARGS);
 }

@@ -101,6 +101,16 @@ __device__ __forceinline__ void tc_mma_f16_elect(uint32_t d_tmem, uint64_t adesc
         "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same for fp32 operands read as TF32 (the low 13 mantissa bits are ignored).
+__device__ __forceinline__ void tc_mma_tf32_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                                  uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p, e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -120,15 +130,17 @@ __device__ __forceinline__ void st_global_32B(void* p, const uint32_t* u) {
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), sm_100
-// descriptor version 1.  Offsets are in bytes; the fields drop the 4 LSBs.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+// Shared-memory matrix descriptor, sm_100 descriptor version 1.  Layout type 2 = 128-byte swizzle
+// (16-byte granules), 1 = 128-byte swizzle with 32-byte granules (the form MN-major 32-bit
+// operands need).  Offsets are in bytes; the fields drop the 4 LSBs.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo,
+                                                   uint32_t layout_type = 2) {
     uint64_t d = 0;
     d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
     d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
     d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
     d |= 1ull << 46;
-    d |= 2ull << 61;
+    d |= (uint64_t)layout_type << 61;
     return d;
 }
 
@@ -162,23 +174,30 @@ inline EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-// 2-D view (n_blocks * bs rows, bs columns) of a compressed tensor, boxes of
-// box_rows (default bs) rows x 64 columns, 128-byte swizzle.
+// 2-D view (n_blocks * bs rows, bs columns) of a compressed tensor.  A box is 128 bytes wide (64
+// 16-bit or 32 fp32 columns) and `box_rows` rows high: the whole block for an operand read K-major,
+// one 128-byte-square atom for one read MN-major.  128-byte swizzle; fp32 atoms read MN-major use
+// the variant with 32-byte granules that their shared-memory descriptor expects.
 inline int make_block_map(CUtensorMap* map, const void* base, int64_t n_blocks, int bs, int dtype,
-                          int box_rows = 0) {
+                          bool mn_major) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) {
         set_cuda_error(cudaErrorNotSupported, "cuTensorMapEncodeTiled entry point");
         return BSP_ERR_CUDA;
     }
+    const int esize = dtype == BSP_F32 ? 4 : 2;
+    const int box_cols = 128 / esize;
     cuuint64_t dims[2] = {(cuuint64_t)bs, (cuuint64_t)(n_blocks * bs)};
-    cuuint64_t strides[1] = {(cuuint64_t)bs * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)(box_rows > 0 ? box_rows : bs)};
+    cuuint64_t strides[1] = {(cuuint64_t)bs * esize};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)(mn_major ? box_cols : bs)};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, dtype == BSP_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                    2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUtensorMapDataType type = dtype == BSP_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                   : dtype == BSP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                       : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    const CUtensorMapSwizzle swizzle = (mn_major && dtype == BSP_F32) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                                                     : CU_TENSOR_MAP_SWIZZLE_128B;
+    CUresult r = fn(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
         return BSP_ERR_CUDA;
@@ -187,7 +206,7 @@ inline int make_block_map(CUtensorMap* map, const void* base, int64_t n_blocks, 
 }
 
 inline uint32_t make_idesc(int dtype, int bs, int op) {
-    const uint32_t fmt = dtype == BSP_F16 ? 0u : 1u;
+    const uint32_t fmt = dtype == BSP_F16 ? 0u : dtype == BSP_BF16 ? 1u : 2u;  // f16 / bf16 / tf32
     const uint32_t a_mn = op == BSP_OP_TN ? 1u : 0u;
     const uint32_t b_mn = op != BSP_OP_NT ? 1u : 0u;
     return (1u << 4)                       // fp32 accumulator

@@ -310,7 +310,8 @@ class Product:
 
     def choose(self, bs: int, dtype: torch.dtype, n_a: int, n_b: int) -> tuple[str, int]:
         """(kernel, panel width) for a launch under the current kernel selection."""
-        tensor_core_path = (dtype in (torch.float16, torch.bfloat16) and bs in (64, 128) and n_a > 0 and n_b > 0
+        tensor_core_path = (dtype in (torch.float16, torch.bfloat16, torch.float32) and bs in (64, 128)
+                            and n_a > 0 and n_b > 0
                             and self.pair.n_out > 0 and self.pair.n_pairs > 0)
         if _kernel_choice == "mma" or not tensor_core_path:
             return "mma", 0  # also: without operand blocks only zero blocks are written

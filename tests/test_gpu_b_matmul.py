@@ -43,7 +43,7 @@ def kernel_family(request):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16], ids=["fp32", "fp16", "bf16"])
 def test_matmul_matrix(shape, dtype, kernel_family):
     B, m, n, k, bs, kept = shape
-    if kernel_family != "auto" and (dtype == torch.float32 or bs < 64):
+    if kernel_family != "auto" and bs < 64:
         pytest.skip("auto already selects the mma.sync kernel here")
     for i, out_layout in enumerate(("fast", "ones", "exact")):
         check_case(make_case(B, m, n, k, bs, kept, dtype, seed=1000 + i, out_layout=out_layout))
