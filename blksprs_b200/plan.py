@@ -58,7 +58,7 @@ PANEL_AUTO_BLOCK_SIZES = (64, 128)
 
 
 def set_kernel(name: str) -> None:
-    """Selects the kernel family for later launches: ``"auto"`` (tcgen05 for 16-bit data with block
+    """Selects the kernel family for later launches: ``"auto"`` (tcgen05 for block
     size 64 / 128, with two-block panels where they pay off; mma.sync otherwise), ``"mma"``
     (mma.sync everywhere), ``"umma"`` (tcgen05, single-block steps) or ``"panel"`` (tcgen05,
     two-block panels).  Meant for tests and profiling; all are sm_100a kernels of one library."""
@@ -292,7 +292,7 @@ def run_step_plan(plan: StepPlan, a: Tensor, b: Tensor, bs: int, bias: Tensor | 
 
 class Product:
     """One block-sparse product (forward, dX or dY) of a layout triple: its pair plan and, built on
-    first use for 16-bit data with block size 64 / 128, its step plans."""
+    first use with block size 64 / 128, its step plans."""
 
     def __init__(self, op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor, R: int, K: int, C: int):
         self.op, self.dims = op, (R, K, C)

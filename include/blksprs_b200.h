@@ -215,7 +215,7 @@ int bsp_matmul_mma(const void* a, int64_t n_a, const void* b, int64_t n_b,
                    int bs, int dtype, int op, int32_t* status_word, void* stream);
 
 /* ---- tcgen05 kernel and its step plan ------------------------------------
- * For fp16 / bf16 and bs 64 / 128 the same products run on tcgen05 tensor
+ * For fp16 / bf16 / fp32 (as TF32) and bs 64 / 128 the same products run on tcgen05 tensor
  * cores from a step plan.  A panel is a run of up to `width` (1 or 2) output
  * blocks, consecutive in the output LUT and in the same (batch, row) of the
  * output layout.  The reference kernel (blksprs/ops/matmul.py:148-253) re-loads

@@ -58,5 +58,5 @@ def test_argument_errors_are_reported_without_a_device():
     assert lib.bsp_bias_grad(None, None, -1, 32, 1, None, 0, None) == _cabi.ERR_INVALID_ARG
     assert lib.bsp_sum_chunks(None, 0, 0, 1, None, None) == _cabi.ERR_INVALID_ARG
     assert lib.bsp_sum_chunks(None, 2, 0, 1, None, None) == _cabi.OK
-    assert lib.bsp_umma_max_width(2, 64) == 0 and lib.bsp_umma_max_width(1, 64) == 2
+    assert lib.bsp_umma_max_width(2, 64) == 2 and lib.bsp_umma_max_width(1, 32) == 0 and lib.bsp_umma_max_width(9, 64) == 0
     assert lib.bsp_layout_matmul(None, 0, None, 0, 1, 1, 1, 1, 9, None, None) == _cabi.ERR_INVALID_ARG
