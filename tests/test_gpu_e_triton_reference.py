@@ -81,3 +81,24 @@ def test_transpose_matches_reference(ref):
     o_out, o_layout = ours.ops.transpose(x, lx.to(DEV), bsz)
     assert torch.equal(r_layout, o_layout)
     assert torch.equal(r_out.as_subclass(torch.Tensor), o_out.as_subclass(torch.Tensor))
+
+
+@pytest.mark.parametrize("bsz", [64, 128])
+def test_fp32_tensor_memory_path_matches_reference_tf32(ref, bsz):
+    """fp32 at block size 64 / 128 runs as `kind::tf32` on the tcgen05 kernel: the operands lose the same
+    mantissa bits as in the reference's TF32 `tl.dot`, only the order of the fp32 additions differs."""
+    import blksprs_b200 as ours
+    from gpu_util import make_case
+    case = make_case(3, 8 * bsz, 6 * bsz, 10 * bsz, bsz, 0.5, torch.float32, seed=77 + bsz, out_layout="exact")
+    lx, ly, lo = (case[k].to(DEV) for k in ("lx", "ly", "lo"))
+    results = []
+    for lib in (ref, ours):
+        x = case["x"].to(DEV).requires_grad_(True)
+        y = case["y"].to(DEV).requires_grad_(True)
+        out = lib.ops.matmul(x, lx, y, ly, lo, bsz)
+        out.backward(case["grad"].to(DEV))
+        torch.cuda.synchronize()
+        results.append(tuple(t.detach().as_subclass(torch.Tensor) for t in (out, x.grad, y.grad)))
+    for r, o, what in zip(results[0], results[1], ("out", "grad_x", "grad_y")):
+        assert r.shape == o.shape and r.dtype == o.dtype
+        assert rel_err(o, r.cpu()) <= 1e-4, (what, rel_err(o, r.cpu()))
