@@ -213,7 +213,9 @@ def build_step_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor
         if SCHEDULE == "dynamic":
             target = int(os.environ.get("BLKSPRS_B200_UNIT_COST", UNIT_COST_DYNAMIC.get(bs, 24)))
             # a whole number of units per CTA: equally fast CTAs then finish together
-            per_cta = max(1, min(MAX_UNITS_PER_CTA_DYNAMIC, round(cost / (max(n_ctas, 1) * max(target, heaviest)))))
+            # no floor at the heaviest panel: a panel heavier than a unit just leaves a few units empty,
+            # while larger units would widen the window of output the CTAs work in beyond what L2 holds
+            per_cta = max(1, min(MAX_UNITS_PER_CTA_DYNAMIC, round(cost / (max(n_ctas, 1) * max(target, 1)))))
             n_units = max(1, n_ctas * per_cta)
         else:
             unit_cost = max(UNIT_COST, 4 * heaviest)
