@@ -25,8 +25,8 @@
 //                 finished accumulator group (the G accumulators of a panel, adjacent
 //                 tensor-memory columns) to the epilogue
 //   warps S+1..S+4 epilogue: tcgen05.ld the fp32 accumulators, add the bias row if there is one,
-//                 convert, write the output blocks with 32-byte stores; blocks no step touched
-//                 are written as zeros (or the bias row)
+//                 convert, write the output blocks in whole 32-byte sectors; blocks no step
+//                 touched are written as zeros (or the bias row)
 //
 // The panels are cut into small units that are handed out in order: a CTA starts with unit
 // blockIdx.x and then draws unit numbers from a global counter (or, without one, takes every
@@ -611,6 +611,55 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 continue;
                             }
                             const uint32_t taddr = tmem_base + grp * (G * BS) + q * BS + ((uint32_t)(wq * 32) << 16);
+                            if constexpr (BS == 64) {
+                                // M = 64: the warp's 16 rows x 64 columns in one load; all 32 lanes get data
+                                uint32_t v[32];
+                                tc_ld16x64(taddr, v);
+                                tc_wait_ld();
+                                const int qd = lane & 3;
+                                const int r0 = wq * 16 + (lane >> 2);  // and r0 + 8
+                                if (BIAS && brow) {
+#pragma unroll
+                                    for (int gq = 0; gq < 8; ++gq) {
+                                        const float b0 = (float)__ldg(brow + 8 * gq + 2 * qd);
+                                        const float b1 = (float)__ldg(brow + 8 * gq + 2 * qd + 1);
+                                        v[4 * gq] = __float_as_uint(__uint_as_float(v[4 * gq]) + b0);
+                                        v[4 * gq + 1] = __float_as_uint(__uint_as_float(v[4 * gq + 1]) + b1);
+                                        v[4 * gq + 2] = __float_as_uint(__uint_as_float(v[4 * gq + 2]) + b0);
+                                        v[4 * gq + 3] = __float_as_uint(__uint_as_float(v[4 * gq + 3]) + b1);
+                                    }
+                                }
+                                T* d0 = o + (int64_t)r0 * BS;
+                                T* d1 = d0 + 8 * BS;
+                                if constexpr (sizeof(T) == 4) {
+                                    // a thread's two adjacent columns are 8 bytes; the four threads of a quad
+                                    // fill one 32-byte sector
+#pragma unroll
+                                    for (int gq = 0; gq < 8; ++gq) {
+                                        st_global_8B(d0 + 8 * gq + 2 * qd, v[4 * gq], v[4 * gq + 1]);
+                                        st_global_8B(d1 + 8 * gq + 2 * qd, v[4 * gq + 2], v[4 * gq + 3]);
+                                    }
+                                } else {
+                                    // 16-bit data: a thread's two columns are one 4-byte word.  Neighbouring
+                                    // lanes swap words of neighbouring column groups, so that every thread
+                                    // stores 8 bytes and a quad again fills whole 32-byte sectors.
+                                    const bool odd = qd & 1;
+#pragma unroll
+                                    for (int gq = 0; gq < 8; gq += 2) {
+                                        const uint32_t a0 = pack2<T>(__uint_as_float(v[4 * gq]), __uint_as_float(v[4 * gq + 1]));
+                                        const uint32_t a1 = pack2<T>(__uint_as_float(v[4 * gq + 2]), __uint_as_float(v[4 * gq + 3]));
+                                        const uint32_t c0 = pack2<T>(__uint_as_float(v[4 * gq + 4]), __uint_as_float(v[4 * gq + 5]));
+                                        const uint32_t c1 = pack2<T>(__uint_as_float(v[4 * gq + 6]), __uint_as_float(v[4 * gq + 7]));
+                                        // even lanes keep group gq and take the neighbour's word of it; odd lanes
+                                        // keep group gq + 1
+                                        const uint32_t x0 = __shfl_xor_sync(0xffffffffu, odd ? a0 : c0, 1);
+                                        const uint32_t x1 = __shfl_xor_sync(0xffffffffu, odd ? a1 : c1, 1);
+                                        const int word = odd ? 4 * (gq + 1) + (qd - 1) : 4 * gq + qd;  // first of the two words
+                                        st_global_8B(reinterpret_cast<uint32_t*>(d0) + word, odd ? x0 : a0, odd ? c0 : x0);
+                                        st_global_8B(reinterpret_cast<uint32_t*>(d1) + word, odd ? x1 : a1, odd ? c1 : x1);
+                                    }
+                                }
+                            } else {
 #pragma unroll
                             for (int c0 = 0; c0 < BS; c0 += 32) {
                                 uint32_t v[32];
@@ -656,6 +705,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                     }
                                 }
                             }
+                                                    }
                         }
                         tc_fence_before();
                         __syncwarp();
