@@ -96,3 +96,19 @@ def test_matches_reference_softmax():
         res.append((out.detach().as_subclass(torch.Tensor), xd.grad))
     assert torch.allclose(res[0][0], res[1][0], atol=1e-6, rtol=1e-5)
     assert torch.allclose(res[0][1], res[1][1], atol=1e-6, rtol=1e-4)
+
+
+def test_very_wide_block_rows_use_the_plain_kernels():
+    """More block columns than a CTA lists in shared memory (8192): the one-warp-per-row kernels take over."""
+    import blksprs_b200 as bs
+    bsz, C = 16, 8200
+    g = torch.Generator().manual_seed(3)
+    layout = (torch.rand((1, 2, C), generator=g) < 0.5)
+    x = torch.randn((int(layout.sum()), bsz, bsz), generator=g) * 2
+    xd = x.to(DEV).requires_grad_(True)
+    out = bs.ops.softmax(xd, layout.to(DEV), bsz)
+    want = oracle.softmax(x, layout, bsz)
+    assert torch.allclose(out.detach().cpu().as_subclass(torch.Tensor), want, atol=1e-6, rtol=1e-5)
+    grad = torch.randn(out.shape, generator=g)
+    out.backward(grad.to(DEV))
+    assert torch.allclose(xd.grad.cpu(), oracle.softmax_backward(grad, want, layout, bsz), atol=1e-6, rtol=1e-4)
