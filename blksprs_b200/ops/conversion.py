@@ -80,21 +80,28 @@ class _ToSparse(torch.autograd.Function):
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, grad_output: Tensor):
-        grad = to_dense(grad_output.contiguous(), ctx.sparsity_layout, ctx.sparsity_block_size)
+        # the scatter itself: the gradient's shape is the output's, so the op's input checks (and the
+        # device reads they need) have nothing to find
+        layout = ctx.sparsity_layout
+        grad = _scatter_blocks(grad_output.contiguous(), build_packed_indices(layout), layout.shape,
+                               ctx.sparsity_block_size, 0)
         return grad, None, None, None, None
 
 
 class _ToDense(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: Tensor, sparsity_layout: Tensor, packed_indices: Tensor, bs: int, fill_value):
-        ctx.sparsity_layout, ctx.sparsity_block_size = sparsity_layout, bs
+        ctx.sparsity_layout, ctx.sparsity_block_size, ctx.n_blocks = sparsity_layout, bs, x.size(0)
         return _scatter_blocks(x, packed_indices, sparsity_layout.shape, bs, fill_value)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, grad_output: Tensor):
-        grad = to_sparse(grad_output.contiguous(), ctx.sparsity_layout, ctx.sparsity_block_size)
-        return grad.as_subclass(Tensor), None, None, None, None
+        # the gather itself; the number of blocks is the forward input's, no device read needed
+        layout = ctx.sparsity_layout
+        lut = build_layout_indices(layout, ctx.n_blocks)
+        grad = _gather_blocks(grad_output.contiguous(), lut, ctx.n_blocks, ctx.sparsity_block_size)
+        return grad, None, None, None, None
 
 
 def _single_full_block(sparsity_layout: Tensor) -> bool:
