@@ -39,9 +39,9 @@ METRIC = "block-sparse matmul effective TFLOP/s (nnz-block FLOPs), forward+backw
 N_BUFFER_SETS = 4
 
 # DRAM bytes (read + write) of one forward launch of the default workload (config2), from the ncu
-# capture summarised in profiles/matmul_umma_kernel_config2.md: 68.7 MB read + 75.0 MB written (the
+# capture summarised in profiles/matmul_umma_kernel_config2.md: 68.7 MB read + 73.5 MB written (the
 # capture replays one launch on the same buffers, so part of the data is served from L2).
-FWD_KERNEL_DRAM_TRAFFIC_BYTES = {"config2": 143.7e6}
+FWD_KERNEL_DRAM_TRAFFIC_BYTES = {"config2": 142.2e6}
 
 
 # ---------------------------------------------------------------------------------------------
