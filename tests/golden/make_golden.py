@@ -21,7 +21,9 @@ import sys
 
 os.environ["TRITON_INTERPRET"] = "1"
 os.environ.setdefault("BLKSPRS_AUTOTUNE", "TEST")
-REF = os.environ.get("BLKSPRS_REFERENCE", "/root/reference")
+REF = os.environ.get("BLKSPRS_REFERENCE")
+if not REF:
+    raise SystemExit("set BLKSPRS_REFERENCE to the checkout of the reference blksprs package")
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
