@@ -65,3 +65,36 @@ def test_work_model_matches_bruteforce():
     brute = sum(int(lx[b, i, k] and ly[b, k, j]) for b in range(2) for i in range(5) for j in range(4)
                 for k in range(6))
     assert oracle.pair_count(lx, ly, lo) == brute
+
+
+def test_linear_and_softmax_restatements_match_their_dense_definitions():
+    """``oracle.linear`` / ``oracle.softmax`` are the dense forms the reference's own tests check against
+    (``torch.nn.Linear`` on the expanded input, test/cases/test_blocksparse.py:1158-1184; softmax over a row's
+    active blocks, blksprs/ops/softmax.py:58-61): here against plain torch on a case with full layouts."""
+    g = torch.Generator().manual_seed(4)
+    bs, B, R, K, N = 16, 2, 3, 2, 4
+    layout = torch.ones((B, R, K), dtype=torch.bool)
+    dense = torch.randn((B, R * bs, K * bs), generator=g)
+    x = oracle.to_sparse(dense, layout, bs)
+    weight, bias = torch.randn((N * bs, K * bs), generator=g), torch.randn(N * bs, generator=g)
+    out, out_layout = oracle.linear(x, layout, bs, weight, bias)
+    want = torch.nn.functional.linear(dense, weight, bias)
+    assert out_layout.shape == (B, R, N) and out_layout.all()
+    assert torch.allclose(oracle.to_dense(out, out_layout, bs), want, atol=1e-5)
+    grad = torch.randn(out.shape, generator=g)
+    dense_req, w_req, b_req = (t.clone().requires_grad_(True) for t in (dense, weight, bias))
+    torch.nn.functional.linear(dense_req, w_req, b_req).backward(oracle.to_dense(grad, out_layout, bs))
+    gx, gw, gb = oracle.linear_backward(grad, out_layout, x, layout, bs, weight, True)
+    assert torch.allclose(oracle.to_dense(gx, layout, bs), dense_req.grad, atol=1e-4)
+    assert torch.allclose(gw, w_req.grad, atol=1e-4) and torch.allclose(gb, b_req.grad, atol=1e-4)
+    # without a bias only the block rows that hold an input block appear in the output
+    sparse_layout = torch.tensor([[[1, 0], [0, 0], [0, 1]], [[0, 0], [1, 1], [0, 0]]], dtype=torch.bool)
+    xs = oracle.to_sparse(dense, sparse_layout, bs)
+    _, lo = oracle.linear(xs, sparse_layout, bs, weight)
+    assert np.array_equal(lo[..., 0], sparse_layout.any(-1).numpy()) and (lo == lo[..., :1]).all()
+    # softmax
+    sm = oracle.softmax(x, layout, bs)
+    assert torch.allclose(oracle.to_dense(sm, layout, bs), torch.softmax(dense, -1), atol=1e-6)
+    masked = oracle.to_dense(oracle.softmax(xs, sparse_layout, bs), sparse_layout, bs)
+    rows_with_blocks = torch.from_numpy(np.repeat(sparse_layout.any(-1).numpy(), bs, axis=1))
+    assert torch.allclose(masked.sum(-1)[rows_with_blocks], torch.ones(int(rows_with_blocks.sum())), atol=1e-5)
