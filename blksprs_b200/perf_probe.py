@@ -2,7 +2,9 @@
 
 ``python -m blksprs_b200.perf_probe softmax|conversion [--small]`` prints one line per case with the
 achieved bandwidth (algorithmic bytes / CUDA-event time).  ``--small`` runs one case of a few hundred
-MB, the size used for profiler captures.
+MB, the size used for profiler captures.  ``python -m blksprs_b200.perf_probe matmul`` times the public
+matmul op (forward, forward + backward) for every dtype and block size on a 16 x 2048^3 problem with
+25 % dense random layouts.
 """
 from __future__ import annotations
 
@@ -75,13 +77,40 @@ def conversion(small: bool, iters: int) -> None:
     bs.utils.enable_validation()
 
 
+def matmul(small: bool, iters: int) -> None:
+    bs.utils.disable_validation()
+    B, n, kept = (4 if small else 16), 2048, 0.25
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        for bsz in (16, 32, 64, 128):
+            g = torch.Generator().manual_seed(1)
+            lx = (torch.rand((B, n // bsz, n // bsz), generator=g) < kept).cuda()
+            ly = (torch.rand((B, n // bsz, n // bsz), generator=g) < kept).cuda()
+            lo = bs.layouting.build_sparsity_layout_matmul(lx, ly)
+            x = torch.randn((int(lx.sum()), bsz, bsz), device="cuda", dtype=dtype)
+            y = torch.randn((int(ly.sum()), bsz, bsz), device="cuda", dtype=dtype)
+            flops = 2.0 * float((lx.float() @ ly.float())[lo].sum()) * bsz ** 3
+            cache = {}
+            xs, ys = x.clone().requires_grad_(True), y.clone().requires_grad_(True)
+            grad = torch.randn_like(bs.ops.matmul(xs, lx, ys, ly, lo, bsz, cache)).as_subclass(torch.Tensor)
+
+            def step():
+                xs.grad = ys.grad = None
+                bs.ops.matmul(xs, lx, ys, ly, lo, bsz, cache).backward(grad)
+
+            fwd = _time(lambda: bs.ops.matmul(x, lx, y, ly, lo, bsz, cache), iters)
+            both = _time(step, iters)
+            print(f"matmul {str(dtype)[6:]} bs={bsz}: forward {fwd * 1e3:.0f} us = {flops / fwd / 1e9:.0f} TFLOP/s  "
+                  f"forward+backward {both * 1e3:.0f} us = {3 * flops / both / 1e9:.0f} TFLOP/s")
+    bs.utils.enable_validation()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["softmax", "conversion"])
+    ap.add_argument("what", choices=["softmax", "conversion", "matmul"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
-    {"softmax": softmax, "conversion": conversion}[args.what](args.small, args.iters)
+    {"softmax": softmax, "conversion": conversion, "matmul": matmul}[args.what](args.small, args.iters)
 
 
 if __name__ == "__main__":
