@@ -1,14 +1,13 @@
-"""Small timing probes of the data-movement kernels around the matmul (conversion, softmax).
+"""Small timing probes of the kernels around the matmul (conversion, softmax) and of the public
+matmul op over every dtype and block size; run through ``bench.py``.
 
-``python -m blksprs_b200.perf_probe softmax|conversion [--small]`` prints one line per case with the
-achieved bandwidth (algorithmic bytes / CUDA-event time).  ``--small`` runs one case of a few hundred
-MB, the size used for profiler captures.  ``python -m blksprs_b200.perf_probe matmul`` times the public
-matmul op (forward, forward + backward) for every dtype and block size on a 16 x 2048^3 problem with
-25 % dense random layouts.
+``python bench.py --probe softmax|conversion [--small]`` prints one line per case with the achieved
+bandwidth (algorithmic bytes / CUDA-event time).  ``--small`` runs one case of a few hundred MB, the
+size used for profiler captures.  ``python bench.py --probe matmul`` times the public matmul op
+(forward, forward + backward) for every dtype and block size on a 16 x 2048^3 problem with 25 %
+dense random layouts.
 """
 from __future__ import annotations
-
-import argparse
 
 import torch
 
@@ -104,14 +103,8 @@ def matmul(small: bool, iters: int) -> None:
     bs.utils.enable_validation()
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["softmax", "conversion", "matmul"])
-    ap.add_argument("--small", action="store_true")
-    ap.add_argument("--iters", type=int, default=10)
-    args = ap.parse_args()
-    {"softmax": softmax, "conversion": conversion, "matmul": matmul}[args.what](args.small, args.iters)
+PROBES = {"softmax": softmax, "conversion": conversion, "matmul": matmul}
 
 
-if __name__ == "__main__":
-    main()
+def run(what: str, small: bool, iters: int) -> None:
+    PROBES[what](small, iters)

@@ -518,8 +518,10 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 if (lane == 0) PROF_STORE(4, w_tempty);
                 if (lane == 0) PROF_STORE(5, w_issue);
                 if (lane == 0) PROF_STORE(6, w_commit);
+                // every MMA issued so far has to complete before tensor memory may be freed; this wait has
+                // its own limit and does not give up early because another role has aborted
                 tc_commit_elect(drain_bar);
-                mbar_wait(drain_bar, 0, abort_flag, status_word);
+                mbar_wait_slow(drain_bar, 0, abort_flag, status_word, kWaitLimitNs, false);
             }
         } else {
             // ---------------- epilogue ----------------

@@ -40,15 +40,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(done) : "r"(bar), "r"(parity) : "memory");
     return done != 0;
 }
-// Bounded wait: false if the limit ran out or another role already gave up.
+// Bounded wait: false if the limit ran out or (unless `honor_abort` is off) another role already
+// gave up.  The drain of outstanding work before tensor memory is freed keeps waiting up to its own
+// limit even after an abort: the MMAs and copies in flight still have to land.
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                             int32_t* status_word,
-                                            unsigned long long limit_ns = kWaitLimitNs) {
+                                            unsigned long long limit_ns = kWaitLimitNs,
+                                            bool honor_abort = true) {
     const unsigned long long t0 = global_timer();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 0xff) == 0) {
-            if (*abort_flag) return false;
+            if (honor_abort && *abort_flag) return false;
             if (global_timer() - t0 > limit_ns) {
                 *abort_flag = 1;
                 if (status_word) *status_word = BSP_ERR_DEVICE_TIMEOUT;

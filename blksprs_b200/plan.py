@@ -113,7 +113,7 @@ def build_pair_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor
                     "bsp_plan_count")
         _cabi.check(lib.bsp_plan_offsets(_cabi.ptr(counts), n_out, _cabi.ptr(offsets), _cabi.ptr(total),
                                          _cabi.ptr(ws), ws_bytes, stream), "bsp_plan_offsets")
-        n_pairs = int(total.item())
+        n_pairs = read_with_status(total, device)[0]
         if n_pairs > 2_147_483_647:
             raise ValueError("blksprs_b200: pair plan exceeds 2^31-1 block pairs")
         pairs = torch.empty((max(n_pairs, 1), 2), dtype=torch.int32, device=device)
@@ -149,17 +149,33 @@ class StepPlan:
         return args
 
     def sched_ptr(self, stream: int) -> int | None:
-        """The scheduling counters (int32[2], zero between launches) of this plan for launches on ``stream``.
-        Launches of one stream run one after the other and may share a pair; every other stream gets its own,
-        so that concurrent launches of one plan never draw from the same counter."""
+        """The scheduling counters (int32[2], zero between launches) for a launch on ``stream``, or
+        None for the static round-robin schedule.  Launches of one stream run one after the other and
+        share a pair; every other stream gets its own, and every launch recorded during a CUDA-graph
+        capture gets a pair of its own (a replayed graph may overlap anything launched later), so that
+        concurrent launches of one plan never draw from the same counter.  A graph must not be
+        replayed concurrently with itself.  The pairs come from a pool allocated with the plan; when
+        it is used up, launches fall back to the static schedule."""
         if not self.dynamic:
             return None
+        pool: Tensor = self.__dict__["_sched_pool"]
         table = self.__dict__.setdefault("_sched", {})
-        counters = table.get(stream)
-        if counters is None:
-            counters = torch.zeros(2, dtype=torch.int32, device=self.steps.device)
-            table[stream] = counters
-        return counters.data_ptr()
+        if torch.cuda.is_current_stream_capturing():
+            slot = len(table)
+            if 2 * slot + 2 > pool.numel():
+                return None
+            table[("capture", slot)] = slot
+            return pool.data_ptr() + 8 * slot
+        slot = table.get(stream)
+        if slot is None:
+            slot = len(table)
+            if 2 * slot + 2 > pool.numel():
+                return None
+            table[stream] = slot
+        return pool.data_ptr() + 8 * slot
+
+
+SCHED_POOL_PAIRS = 64
 
 
 def build_step_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor, R: int, K: int, C: int,
@@ -199,7 +215,7 @@ def build_step_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor
         _cabi.check(lib.bsp_plan_offsets(_cabi.ptr(counts), n_panels, _cabi.ptr(offsets), _cabi.ptr(total),
                                          _cabi.ptr(ws), ws_bytes, stream), "bsp_plan_offsets")
         largest = counts[:n_panels].max().to(torch.int64).reshape(1) if n_panels else total
-        n_steps, max_panel_steps = (int(v) for v in torch.cat([total, largest]).tolist())
+        n_steps, max_panel_steps = read_with_status(torch.cat([total, largest]), device)
         if n_steps > 2_147_483_647 // 8:
             raise ValueError("blksprs_b200: step plan too large")
         steps = torch.empty((max(n_steps, 1), 8), dtype=torch.int32, device=device)
@@ -225,11 +241,25 @@ def build_step_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor
         _cabi.check(lib.bsp_plan_schedule(_cabi.ptr(offsets), n_panels, BLOCK_COST * width, n_units,
                                           _cabi.ptr(unit_panel), stream), "bsp_plan_schedule")
         unit_step = offsets[unit_panel.long()].contiguous()
-    return StepPlan(op, n_out, n_panels, n_steps, width, panel_first, offsets, steps, touched, unit_panel,
-                    unit_step, n_units, SCHEDULE == "dynamic")
+        plan = StepPlan(op, n_out, n_panels, n_steps, width, panel_first, offsets, steps, touched, unit_panel,
+                        unit_step, n_units, SCHEDULE == "dynamic")
+        plan.__dict__["_sched_pool"] = torch.zeros(2 * SCHED_POOL_PAIRS, dtype=torch.int32, device=device)
+    return plan
 
 
 _status_words: dict[torch.device, Tensor] = {}
+
+
+def read_with_status(values: Tensor, device: torch.device) -> list[int]:
+    """Reads int64 device values to the host together with the device status word (one copy, one
+    sync): wherever the host has to wait for the device anyway, a problem an earlier kernel recorded
+    (``BSP_ERR_DEVICE_RANGE``, ``BSP_ERR_DEVICE_TIMEOUT``) surfaces as an exception."""
+    word = status_word(device)
+    *out, code = torch.cat([values.reshape(-1).to(torch.int64), word.to(torch.int64)]).tolist()
+    if code != 0:
+        word.zero_()
+        raise _cabi.NativeError(int(code), "device status word (set by an earlier kernel)")
+    return [int(v) for v in out]
 
 
 def status_word(device: torch.device) -> Tensor:

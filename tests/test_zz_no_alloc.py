@@ -56,6 +56,27 @@ def test_static_scratch_entry_point_matches_regular_one_twice_in_a_row():
         assert int(got_total) == int((layout != 0).sum())
 
 
+@pytest.mark.parametrize("numel", ["limit", 2048 * 37 + 1, 2048, 2049])
+def test_static_scratch_entry_point_at_its_size_limit_and_at_partial_chunks(numel):
+    """The largest accepted layout fills every slot of the fixed scratch array (one chunk sum per 2048
+    entries plus the total); sizes one past a chunk boundary leave a partial last chunk."""
+    from blksprs_b200 import _cabi as cabi
+    lib = cabi.lib()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    if numel == "limit":
+        numel = lib.bsp_static_scratch_max_numel()
+    g = torch.Generator(device=dev).manual_seed(7)
+    layout = torch.rand((numel,), generator=g, device=dev) < 0.4
+    layout[-1] = True   # the last entry's rank depends on every chunk sum before it
+    want_packed, want_total = _regular(lib, cabi, layout)
+    got_packed, got_total = _static(lib, cabi, layout)
+    torch.cuda.synchronize()
+    assert torch.equal(got_packed, want_packed)
+    assert torch.equal(got_total, want_total)
+    assert int(got_packed[-1]) == int(got_total) - 1
+
+
 def test_static_scratch_entry_point_rejects_oversized_layouts():
     from blksprs_b200 import _cabi as cabi
     lib = cabi.lib()
