@@ -4,12 +4,22 @@
 // blksprs/ops/matmul.py:242), and any other (dtype, bs) when asked for by
 // BSP_KERNEL_MMA.
 //
-// One CTA computes one TILE x TILE tile of one output block.  Per (pair,
-// k-chunk) step the two operand tiles are copied global -> shared with
-// cp.async, double buffered, always in their global orientation; whether an
-// operand is read transposed (BSP_OP_NT / BSP_OP_TN) is decided when the
-// fragments are read from shared memory (ldmatrix[.trans] for 16-bit data,
-// scalar loads for fp32).
+// Two kernels.
+//
+// matmul_mma_stream_kernel (block sizes 16 and 32): persistent CTAs of four warps; every warp
+// works on its own.  A warp takes chunks of up to 32 consecutive output blocks; the pairs of those
+// blocks are one contiguous range of the pair list, which the warp streams through a ring of
+// cp.async stages of its own (one stage = the two operand blocks of a pair), several pairs ahead
+// and across output-block boundaries, with the pair records themselves fetched 32 at a time.
+// Block boundaries come from the offsets array.  No CTA-wide barrier exists in the loop; a
+// block's result goes from the accumulator fragments straight to global memory.
+//
+// matmul_mma_kernel (any block size; used for >= 64 when this family is asked for): one CTA
+// computes one TILE x TILE tile of one output block, double-buffered cp.async per (pair, k-chunk).
+//
+// Operand tiles are always copied in their global orientation; whether an operand is read
+// transposed (BSP_OP_NT / BSP_OP_TN) is decided when the fragments are read from shared memory
+// (ldmatrix[.trans] for 16-bit data, scalar loads for fp32).
 #include "common.cuh"
 
 namespace bsp {
@@ -239,6 +249,270 @@ matmul_mma_kernel(const T* __restrict__ a, int64_t n_a, const T* __restrict__ b,
         }
 }
 
+
+// ---- warp-autonomous streaming kernel for block sizes 16 and 32 ----------------------------
+
+template <typename T, int BS> struct StreamCfg {
+    // ring depth per warp: the tiles are small, so depth is what hides the L2 / HBM latency
+    static constexpr int kStages = sizeof(T) == 2 ? (BS == 16 ? 8 : 4) : (BS == 16 ? 6 : 2);
+    static constexpr int kWarps = 4;
+};
+
+template <typename T, int BS, int OP>
+__global__ void __launch_bounds__(128)
+matmul_mma_stream_kernel(const T* __restrict__ a, int64_t n_a, const T* __restrict__ b, int64_t n_b,
+                         T* __restrict__ out, const int32_t* __restrict__ offsets,
+                         const int32_t* __restrict__ pairs, int n_out, int chunk,
+                         int32_t* __restrict__ status_word) {
+    constexpr bool A_TRANS = (OP == BSP_OP_TN);  // shared A tile holds [k][m]
+    constexpr bool B_NK = (OP == BSP_OP_NT);     // shared B tile holds [n][k]
+    constexpr int S = StreamCfg<T, BS>::kStages;
+    constexpr int MI = BS / 16, NI = BS / 8;
+    constexpr int APAD = Pad<T, !A_TRANS>::value, BPAD = Pad<T, B_NK>::value;
+    constexpr int ALD = BS + APAD, BLD = BS + BPAD;
+    constexpr int KSTEP = Elem<T>::k16 ? 16 : 8;
+    constexpr int CHUNK = 16 / sizeof(T);        // elements per 16-byte copy
+    constexpr int CPR = BS / CHUNK;              // 16-byte copies per tile row
+    constexpr int STAGE_ELEMS = BS * (ALD + BLD);
+    constexpr int64_t BLK = (int64_t)BS * BS;
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    T* ring = reinterpret_cast<T*>(smem_raw) + (size_t)warp * S * STAGE_ELEMS;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int total_warps = gridDim.x * StreamCfg<T, BS>::kWarps;
+    const int n_chunks = (n_out + chunk - 1) / chunk;
+
+    float acc[MI][NI][4];
+    auto clear_acc = [&]() {
+#pragma unroll
+        for (int i = 0; i < MI; ++i)
+#pragma unroll
+            for (int j = 0; j < NI; ++j)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) acc[i][j][r] = 0.f;
+    };
+    auto write_block = [&](int64_t p) {
+        T* o = out + p * BLK;
+#pragma unroll
+        for (int i = 0; i < MI; ++i)
+#pragma unroll
+            for (int j = 0; j < NI; ++j) {
+                const int row = i * 16 + g, col = j * 8 + 2 * t4;
+                Elem<T>::store2(o + row * BS + col, acc[i][j][0], acc[i][j][1]);
+                Elem<T>::store2(o + (row + 8) * BS + col, acc[i][j][2], acc[i][j][3]);
+            }
+    };
+
+    for (int c = blockIdx.x * StreamCfg<T, BS>::kWarps + warp; c < n_chunks; c += total_warps) {
+        const int p0 = c * chunk;
+        const int nb = min(chunk, n_out - p0);
+        // lane l holds the offset of block p0 + l (chunk <= 32); the range's end is read by all
+        const int my_off = offsets[p0 + min(lane, nb)];
+        const int q_begin = __shfl_sync(0xffffffffu, my_off, 0);
+        const int q_end = offsets[p0 + nb];
+        const int n_pairs = q_end - q_begin;
+
+        // pair records, 32 at a time: this window and the next one
+        auto load_window = [&](int w) -> int2 {
+            const int q = q_begin + w * 32 + lane;
+            if (q < q_end) return *reinterpret_cast<const int2*>(pairs + 2 * (int64_t)q);
+            return make_int2(-1, -1);
+        };
+        // `win` holds the window the copies are being issued from, `win_next` the one after it (in
+        // flight for 32 issues before its first record is needed)
+        int2 win = load_window(0), win_next = load_window(1);
+        int win_no = 0;
+        auto record = [&](int s, int& ia, int& ib) {
+            if ((s >> 5) > win_no) {
+                win = win_next;
+                ++win_no;
+                win_next = load_window(win_no + 1);
+            }
+            const int xa = __shfl_sync(0xffffffffu, win.x, s & 31);
+            const int xb = __shfl_sync(0xffffffffu, win.y, s & 31);
+            ia = xa < 0 ? -1 : (xa & 0x3fffffff);  // bit 30 marks a block's last pair (not used here)
+            ib = xb;
+        };
+        // copies the two operand blocks of stream position s into its ring stage; the validity of
+        // the indices is returned (nothing is copied for a bad pair)
+        auto issue = [&](int s) -> bool {
+            int ia, ib;
+            record(s, ia, ib);
+            const bool ok = ia >= 0 && ia < n_a && ib >= 0 && ib < n_b;
+            if (ok) {
+                const T* ga = a + ia * BLK;
+                const T* gb = b + ib * BLK;
+                T* sa = ring + (s % S) * STAGE_ELEMS;
+                T* sb = sa + BS * ALD;
+#pragma unroll
+                for (int i = lane; i < BS * CPR; i += 32) {
+                    const int r = i / CPR, cc = (i % CPR) * CHUNK;
+                    cp_async16(sa + r * ALD + cc, ga + r * BS + cc);
+                    cp_async16(sb + r * BLD + cc, gb + r * BS + cc);
+                }
+            } else if (status_word && lane == 0) {
+                *status_word = BSP_ERR_DEVICE_RANGE;
+            }
+            cp_async_commit();
+            return ok;
+        };
+
+        clear_acc();
+        int blk = 0;  // current block, relative to p0
+        // stream position at which block `bl` ends: the offsets of blocks p0 .. p0 + nb - 1 are in the
+        // lanes, the last block ends with the range
+        auto block_end = [&](int bl) {
+            const int e = __shfl_sync(0xffffffffu, my_off, min(bl + 1, 31));
+            return bl + 1 >= nb ? n_pairs : e - q_begin;
+        };
+        int blk_end = block_end(0);
+
+        uint32_t ok_mask = 0;  // bit (s % 32): pair s had valid indices
+        const int lead = min(S - 1, n_pairs);
+        for (int s = 0; s < lead; ++s) ok_mask |= (issue(s) ? 1u : 0u) << (s & 31);
+        for (int s = 0; s < n_pairs; ++s) {
+            // blocks that end before this pair (the previous pair's block, and empty ones) are written
+            while (s == blk_end && blk < nb) {
+                write_block(p0 + blk);
+                clear_acc();
+                ++blk;
+                blk_end = block_end(blk);
+            }
+            const int sn = s + S - 1;
+            if (sn < n_pairs) {
+                const bool okn = issue(sn);
+                ok_mask = (ok_mask & ~(1u << (sn & 31))) | ((okn ? 1u : 0u) << (sn & 31));
+                cp_async_wait<S - 1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncwarp();
+            if ((ok_mask >> (s & 31)) & 1u) {
+                const T* sa = ring + (s % S) * STAGE_ELEMS;
+                const T* sb = sa + BS * ALD;
+#pragma unroll
+                for (int k0 = 0; k0 < BS; k0 += KSTEP) {
+                    uint32_t af[MI][4];
+                    uint32_t bf[NI][2];
+                    if constexpr (Elem<T>::k16) {
+                        const int q = lane >> 3, rr = lane & 7;
+#pragma unroll
+                        for (int i = 0; i < MI; ++i) {
+                            const int m0 = i * 16;
+                            if constexpr (!A_TRANS) {
+                                ldmatrix_x4(af[i], sa + (m0 + rr + (q & 1) * 8) * ALD + k0 + (q >> 1) * 8);
+                            } else {
+                                ldmatrix_x4_trans(af[i], sa + (k0 + rr + (q >> 1) * 8) * ALD + m0 + (q & 1) * 8);
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < NI; j += 2) {
+                            const int n0 = j * 8;
+                            uint32_t r4[4];
+                            if constexpr (B_NK) {
+                                ldmatrix_x4(r4, sb + (n0 + rr + (q >> 1) * 8) * BLD + k0 + (q & 1) * 8);
+                            } else {
+                                ldmatrix_x4_trans(r4, sb + (k0 + rr + (q & 1) * 8) * BLD + n0 + (q >> 1) * 8);
+                            }
+                            bf[j][0] = r4[0]; bf[j][1] = r4[1];
+                            bf[j + 1][0] = r4[2]; bf[j + 1][1] = r4[3];
+                        }
+                    } else {
+                        auto A_at = [&](int m, int k) -> float {
+                            return A_TRANS ? (float)sa[k * ALD + m] : (float)sa[m * ALD + k];
+                        };
+                        auto B_at = [&](int k, int n) -> float {
+                            return B_NK ? (float)sb[n * BLD + k] : (float)sb[k * BLD + n];
+                        };
+#pragma unroll
+                        for (int i = 0; i < MI; ++i) {
+                            const int m0 = i * 16;
+                            af[i][0] = f32_to_tf32(A_at(m0 + g, k0 + t4));
+                            af[i][1] = f32_to_tf32(A_at(m0 + g + 8, k0 + t4));
+                            af[i][2] = f32_to_tf32(A_at(m0 + g, k0 + t4 + 4));
+                            af[i][3] = f32_to_tf32(A_at(m0 + g + 8, k0 + t4 + 4));
+                        }
+#pragma unroll
+                        for (int j = 0; j < NI; ++j) {
+                            const int n0 = j * 8;
+                            bf[j][0] = f32_to_tf32(B_at(k0 + t4, n0 + g));
+                            bf[j][1] = f32_to_tf32(B_at(k0 + t4 + 4, n0 + g));
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < MI; ++i)
+#pragma unroll
+                        for (int j = 0; j < NI; ++j) Elem<T>::mma(acc[i][j], af[i], bf[j]);
+                }
+            }
+            __syncwarp();  // the stage may be refilled by the next iteration's copies
+        }
+        // the chunk's remaining blocks: the last one with pairs, and empty ones behind it
+        while (blk < nb) {
+            write_block(p0 + blk);
+            clear_acc();
+            ++blk;
+        }
+    }
+}
+
+template <typename T, int BS, int OP>
+static int launch_stream(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out, int64_t n_out,
+                         const int32_t* offsets, const int32_t* pairs, int32_t* status_word, cudaStream_t stream) {
+    constexpr bool A_TRANS = (OP == BSP_OP_TN), B_NK = (OP == BSP_OP_NT);
+    constexpr int ALD = BS + Pad<T, !A_TRANS>::value, BLD = BS + Pad<T, B_NK>::value;
+    constexpr int W = StreamCfg<T, BS>::kWarps;
+    constexpr size_t smem = (size_t)W * StreamCfg<T, BS>::kStages * BS * (ALD + BLD) * sizeof(T);
+    auto kern = matmul_mma_stream_kernel<T, BS, OP>;
+    // per device, looked up once: the shared-memory opt-in, the SM count and the resident CTAs per SM
+    static int cached_sms[64] = {0}, cached_per_sm[64] = {0};
+    int dev = 0;
+    BSP_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return BSP_ERR_UNSUPPORTED;
+    if (cached_sms[dev] == 0) {
+        int n_sm = 0, n_cta = 0;
+        BSP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        BSP_CUDA_TRY(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+        BSP_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n_cta, kern, 32 * W, smem));
+        cached_per_sm[dev] = n_cta < 1 ? 1 : n_cta;
+        cached_sms[dev] = n_sm;
+    }
+    const int sms = cached_sms[dev], per_sm = cached_per_sm[dev];
+    // chunks of consecutive output blocks per warp visit: as large as the block count allows while
+    // every resident warp still gets several chunks (small problems: one block per warp)
+    const int64_t warps = (int64_t)sms * per_sm * W;
+    int64_t chunk = n_out / (warps * 4);
+    chunk = chunk < 1 ? 1 : (chunk > 32 ? 32 : chunk);
+    const int64_t n_chunks = (n_out + chunk - 1) / chunk;
+    int64_t ctas = (n_chunks + W - 1) / W;
+    if (ctas > (int64_t)sms * per_sm) ctas = (int64_t)sms * per_sm;
+    kern<<<(unsigned)ctas, 32 * W, smem, stream>>>((const T*)a, n_a, (const T*)b, n_b, (T*)out, offsets, pairs,
+                                                   (int)n_out, (int)chunk, status_word);
+    BSP_LAUNCH_CHECK();
+    return BSP_OK;
+}
+
+template <typename T, int BS>
+static int launch_stream_op(int op, const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
+                            int64_t n_out, const int32_t* offsets, const int32_t* pairs, int32_t* status_word,
+                            cudaStream_t stream) {
+    switch (op) {
+        case BSP_OP_NN: return launch_stream<T, BS, BSP_OP_NN>(a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+        case BSP_OP_NT: return launch_stream<T, BS, BSP_OP_NT>(a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+        case BSP_OP_TN: return launch_stream<T, BS, BSP_OP_TN>(a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+        default: return BSP_ERR_INVALID_ARG;
+    }
+}
+
+template <typename T>
+static int launch_stream_bs(int bs, int op, const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
+                            int64_t n_out, const int32_t* offsets, const int32_t* pairs, int32_t* status_word,
+                            cudaStream_t stream) {
+    if (bs == 16) return launch_stream_op<T, 16>(op, a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+    return launch_stream_op<T, 32>(op, a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+}
+
 template <typename T, int TILE, int OP>
 static int launch_one(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
                       int64_t n_out, const int32_t* offsets, const int32_t* pairs, int bs,
@@ -288,6 +562,14 @@ int launch_matmul_mma(const void* a, int64_t n_a, const void* b, int64_t n_b, vo
                       int64_t n_out, const int32_t* offsets, const int32_t* pairs, int bs,
                       int dtype, int op, int32_t* status_word, cudaStream_t stream) {
     if (n_out > 0x7fffffffLL) return BSP_ERR_UNSUPPORTED;
+    if (bs == 16 || bs == 32) {
+        switch (dtype) {
+            case BSP_F16: return launch_stream_bs<__half>(bs, op, a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+            case BSP_BF16: return launch_stream_bs<__nv_bfloat16>(bs, op, a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+            case BSP_F32: return launch_stream_bs<float>(bs, op, a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+            default: return BSP_ERR_UNSUPPORTED;
+        }
+    }
     const int tiles_cap = bs / (dtype == BSP_F32 ? 32 : 64);
     if (tiles_cap > 0 && (int64_t)tiles_cap * tiles_cap > 65535) return BSP_ERR_UNSUPPORTED;
     switch (dtype) {

@@ -123,6 +123,47 @@ __device__ __forceinline__ void tc_mma_elect(uint32_t d_tmem, uint64_t adesc, ui
     else tc_mma_f16_elect(d_tmem, adesc, bdesc, idesc, accumulate);
 }
 
+// Exchange inside a quad (lanes 4r .. 4r + 3).  In: thread q holds words w[g], g = 0..7, where word (g, q)
+// lies at byte 16 g + 4 q of a 128-byte row.  Out: thread q holds the eight words of bytes
+// [32 q, 32 q + 32): the word at byte 32 q + 4 j is in slot {0, 2, 4, 6, 1, 3, 5, 7}[j].  Two butterfly
+// stages; a stage pairs lane bit m with slot bit sb: a thread keeps the slots whose bit equals its own
+// and trades the others with its partner, the received word taking the vacated slot.
+__device__ __forceinline__ void quad_gather8(uint32_t (&w)[8], int lane) {
+#pragma unroll
+    for (int stage = 0; stage < 2; ++stage) {
+        const int m = stage == 0 ? 2 : 1, sb = stage == 0 ? 4 : 2;
+        const bool up = (lane & m) != 0;
+#pragma unroll
+        for (int s0 = 0; s0 < 8; ++s0) {
+            if (s0 & sb) continue;
+            const int s1 = s0 | sb;
+            const uint32_t r = __shfl_xor_sync(0xffffffffu, up ? w[s0] : w[s1], m);
+            if (up) w[s0] = r; else w[s1] = r;
+        }
+    }
+}
+
+// Exchange among the 8 lanes of a group (lanes 8 m .. 8 m + 7).  In: lane l holds 8 chunks of 4 words,
+// chunk c of its own row at w[4 c ..].  Out: slot i holds chunk (l & 7) of the row of lane (l & ~7) + i.
+// Three butterfly stages over lane bits 4, 2, 1 (slot bit = lane bit), as in quad_gather8.
+__device__ __forceinline__ void octet_gather_chunks(uint32_t (&w)[32], int lane) {
+#pragma unroll
+    for (int stage = 0; stage < 3; ++stage) {
+        const int m = 4 >> stage;
+        const bool up = (lane & m) != 0;
+#pragma unroll
+        for (int s0 = 0; s0 < 8; ++s0) {
+            if (s0 & m) continue;
+            const int s1 = s0 | m;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t r = __shfl_xor_sync(0xffffffffu, up ? w[4 * s0 + k] : w[4 * s1 + k], m);
+                if (up) w[4 * s0 + k] = r; else w[4 * s1 + k] = r;
+            }
+        }
+    }
+}
+
 template <typename T, int BS, int OP, int G, bool BIAS>
 __global__ void __launch_bounds__(PCfg<BS, G>::kThreads, PCfg<BS, G>::kCtasPerSm)
 matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -642,24 +683,59 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                         st_global_8B(d1 + 8 * gq + 2 * qd, v[4 * gq + 2], v[4 * gq + 3]);
                                     }
                                 } else {
-                                    // 16-bit data: a thread's two columns are one 4-byte word.  Neighbouring
-                                    // lanes swap words of neighbouring column groups, so that every thread
-                                    // stores 8 bytes and a quad again fills whole 32-byte sectors.
-                                    const bool odd = qd & 1;
+                                    // 16-bit data: a thread's two columns are one 4-byte word, the four threads
+                                    // of a quad hold a row's eight column groups interleaved.  A 4 x 4 exchange
+                                    // inside the quad gives every thread 32 contiguous bytes of the row, so that a
+                                    // quad writes the row's whole 128-byte line with one 32-byte store per thread.
+                                    uint32_t wa[8], wb[8];
 #pragma unroll
-                                    for (int gq = 0; gq < 8; gq += 2) {
-                                        const uint32_t a0 = pack2<T>(__uint_as_float(v[4 * gq]), __uint_as_float(v[4 * gq + 1]));
-                                        const uint32_t a1 = pack2<T>(__uint_as_float(v[4 * gq + 2]), __uint_as_float(v[4 * gq + 3]));
-                                        const uint32_t c0 = pack2<T>(__uint_as_float(v[4 * gq + 4]), __uint_as_float(v[4 * gq + 5]));
-                                        const uint32_t c1 = pack2<T>(__uint_as_float(v[4 * gq + 6]), __uint_as_float(v[4 * gq + 7]));
-                                        // even lanes keep group gq and take the neighbour's word of it; odd lanes
-                                        // keep group gq + 1
-                                        const uint32_t x0 = __shfl_xor_sync(0xffffffffu, odd ? a0 : c0, 1);
-                                        const uint32_t x1 = __shfl_xor_sync(0xffffffffu, odd ? a1 : c1, 1);
-                                        const int word = odd ? 4 * (gq + 1) + (qd - 1) : 4 * gq + qd;  // first of the two words
-                                        st_global_8B(reinterpret_cast<uint32_t*>(d0) + word, odd ? x0 : a0, odd ? c0 : x0);
-                                        st_global_8B(reinterpret_cast<uint32_t*>(d1) + word, odd ? x1 : a1, odd ? c1 : x1);
+                                    for (int gq = 0; gq < 8; ++gq) {
+                                        wa[gq] = pack2<T>(__uint_as_float(v[4 * gq]), __uint_as_float(v[4 * gq + 1]));
+                                        wb[gq] = pack2<T>(__uint_as_float(v[4 * gq + 2]), __uint_as_float(v[4 * gq + 3]));
                                     }
+                                    quad_gather8(wa, lane);
+                                    quad_gather8(wb, lane);
+                                    uint32_t oa[8], ob[8];
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) {
+                                        constexpr int kSlot[8] = {0, 2, 4, 6, 1, 3, 5, 7};  // slot holding output word j
+                                        oa[j] = wa[kSlot[j]];
+                                        ob[j] = wb[kSlot[j]];
+                                    }
+                                    st_global_32B(d0 + 16 * qd, oa);
+                                    st_global_32B(d1 + 16 * qd, ob);
+                                }
+                            } else if constexpr (sizeof(T) == 2) {
+                                // 16-bit data, lane = row: 64 columns (two loads) are 128 bytes of a row.  An 8 x 8
+                                // exchange of 16-byte chunks among the 8 lanes of a group leaves every lane with
+                                // the same chunk of the group's 8 rows, so that 8 neighbouring lanes store one
+                                // row's whole 128-byte line per instruction.
+                                T* obase = o + (int64_t)(wq * 32 + (lane & ~7)) * BS + (lane & 7) * 8;
+#pragma unroll
+                                for (int half = 0; half < 2; ++half) {
+                                    uint32_t v[64];
+                                    tc_ld32(taddr + half * 64, v);
+                                    tc_ld32(taddr + half * 64 + 32, v + 32);
+                                    tc_wait_ld();
+                                    if (BIAS && brow) {
+                                        const uint4* bv = reinterpret_cast<const uint4*>(brow + half * 64);
+#pragma unroll
+                                        for (int i = 0; i < 8; ++i) {
+                                            const uint4 b4 = __ldg(bv + i);
+                                            const T* be = reinterpret_cast<const T*>(&b4);
+#pragma unroll
+                                            for (int e = 0; e < 8; ++e)
+                                                v[8 * i + e] = __float_as_uint(__uint_as_float(v[8 * i + e]) + (float)be[e]);
+                                        }
+                                    }
+                                    uint32_t w[32];
+#pragma unroll
+                                    for (int e = 0; e < 32; ++e)
+                                        w[e] = pack2<T>(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
+                                    octet_gather_chunks(w, lane);
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i)
+                                        st_global_16B(obase + (int64_t)i * BS + half * 64, w + 4 * i);
                                 }
                             } else {
 #pragma unroll
@@ -681,29 +757,16 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                     }
                                 }
                                 if (row_valid) {
+                                    // 32 fp32 columns = 128 bytes of the row: four 32-byte stores
                                     T* dst = o + (int64_t)row * BS + c0;
-                                    if constexpr (sizeof(T) == 4) {
-                                        // 32 fp32 columns = 128 bytes of the row: four 32-byte stores
 #pragma unroll
-                                        for (int i = 0; i < 4; ++i) {
-                                            uint32_t w8[8];
+                                    for (int i = 0; i < 4; ++i) {
+                                        uint32_t w8[8];
 #pragma unroll
-                                            for (int e = 0; e < 8; ++e)  // + 0: the vector store gets registers of its
-                                                // own (it cannot take the load's octet in place); -0 becomes +0
-                                                w8[e] = __float_as_uint(__uint_as_float(v[8 * i + e]) + 0.0f);
-                                            st_global_32B(dst + 8 * i, w8);
-                                        }
-                                    } else {
-                                        // 32 columns = 64 bytes of the row: two 32-byte stores, each a whole sector
-#pragma unroll
-                                        for (int i = 0; i < 2; ++i) {
-                                            uint32_t w8[8];
-#pragma unroll
-                                            for (int e = 0; e < 8; ++e)
-                                                w8[e] = pack2<T>(__uint_as_float(v[16 * i + 2 * e]),
-                                                                 __uint_as_float(v[16 * i + 2 * e + 1]));
-                                            st_global_32B(dst + 16 * i, w8);
-                                        }
+                                        for (int e = 0; e < 8; ++e)  // + 0: the vector store gets registers of its
+                                            // own (it cannot take the load's octet in place); -0 becomes +0
+                                            w8[e] = __float_as_uint(__uint_as_float(v[8 * i + e]) + 0.0f);
+                                        st_global_32B(dst + 8 * i, w8);
                                     }
                                 }
                             }

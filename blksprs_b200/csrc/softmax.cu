@@ -218,6 +218,101 @@ softmax_bwd_list_kernel(const float* __restrict__ g, const float* __restrict__ o
     }
 }
 
+// ---- second half of the softmax that is fused into the matmul epilogue -----------------------
+// The matmul kernel's softmax epilogue leaves, per output block p and block row r, e = exp(s - m)
+// with m = the row's maximum inside that block and l = its sum of e (stats[p][r] = (m, l)).  The
+// blocks of one block row of the layout are consecutive in the compressed tensor
+// (blocks [row_first[i], row_first[i + 1]) for block row i), so a CTA takes one block row: first the
+// row-wide maximum M = max_j m_j and sum L = sum_j l_j exp(m_j - M) of every matrix row, then every
+// element once: p = e * exp(m_j - M) / L, converted to the output type.
+template <typename T> __device__ inline float to_f32(T v);
+template <> __device__ inline float to_f32<float>(float v) { return v; }
+template <> __device__ inline float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ inline float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ inline T from_f32(float v);
+template <> __device__ inline float from_f32<float>(float v) { return v; }
+template <> __device__ inline __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ inline __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+softmax_normalize_kernel(const TI* __restrict__ e, const float2* __restrict__ stats,
+                         const int32_t* __restrict__ row_first, int64_t n_block_rows, int bs, int bs_log2,
+                         TO* __restrict__ out) {
+    extern __shared__ float row_scale[];  // [bs] row maximum M, [bs] 1 / L
+    float* row_max = row_scale;
+    float* row_inv = row_scale + bs;
+    constexpr int V = 8;  // elements per thread and step
+    for (int64_t br = blockIdx.x; br < n_block_rows; br += gridDim.x) {
+        const int first = row_first[br], n = row_first[br + 1] - first;
+        if (n <= 0) continue;
+        __syncthreads();  // the previous block row's readers are done with row_scale
+        for (int r = threadIdx.x; r < bs; r += blockDim.x) {
+            const float2* st = stats + (int64_t)first * bs + r;
+            float M = -FLT_MAX;
+            for (int j = 0; j < n; ++j) M = fmaxf(M, st[(int64_t)j * bs].x);
+            float L = 0.f;
+            for (int j = 0; j < n; ++j) {
+                const float2 ml = st[(int64_t)j * bs];
+                L += ml.y * fast_exp(ml.x - M);
+            }
+            row_max[r] = M;
+            row_inv[r] = 1.f / L;
+        }
+        __syncthreads();
+        const int64_t base = (int64_t)first * bs * bs;
+        const int64_t total = (int64_t)n * bs * bs;
+        for (int64_t i = (int64_t)threadIdx.x * V; i < total; i += (int64_t)blockDim.x * V) {
+            const int64_t row_index = i >> bs_log2;             // (block j, matrix row r) = j * bs + r
+            const int r = (int)(row_index & (bs - 1));
+            const float f = fast_exp(stats[(int64_t)first * bs + row_index].x - row_max[r]) * row_inv[r];
+            TI in[V];
+            TO o[V];
+            if constexpr (sizeof(TI) == 2) {
+                *reinterpret_cast<uint4*>(in) = *reinterpret_cast<const uint4*>(e + base + i);
+            } else {
+                *reinterpret_cast<uint4*>(in) = *reinterpret_cast<const uint4*>(e + base + i);
+                *reinterpret_cast<uint4*>(in + 4) = *reinterpret_cast<const uint4*>(e + base + i + 4);
+            }
+#pragma unroll
+            for (int k = 0; k < V; ++k) o[k] = from_f32<TO>(to_f32<TI>(in[k]) * f);
+            if constexpr (sizeof(TO) == 2) {
+                *reinterpret_cast<uint4*>(out + base + i) = *reinterpret_cast<const uint4*>(o);
+            } else {
+                *reinterpret_cast<uint4*>(out + base + i) = *reinterpret_cast<const uint4*>(o);
+                *reinterpret_cast<uint4*>(out + base + i + 4) = *reinterpret_cast<const uint4*>(o + 4);
+            }
+        }
+    }
+}
+
+template <typename TI>
+static int launch_normalize_out(int out_dtype, const void* e, const float* stats, const int32_t* row_first,
+                                int64_t n_block_rows, int bs, void* out, cudaStream_t stream) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t cap = (int64_t)sms * 8;
+    const unsigned grid = (unsigned)(n_block_rows < cap ? n_block_rows : cap);
+    int bs_log2 = 0;
+    while ((1 << bs_log2) < bs) ++bs_log2;
+    const size_t smem = 2 * (size_t)bs * sizeof(float);
+    const float2* st = reinterpret_cast<const float2*>(stats);
+    switch (out_dtype) {
+        case BSP_F16:
+            softmax_normalize_kernel<TI, __half><<<grid, 256, smem, stream>>>((const TI*)e, st, row_first, n_block_rows, bs, bs_log2, (__half*)out);
+            break;
+        case BSP_BF16:
+            softmax_normalize_kernel<TI, __nv_bfloat16><<<grid, 256, smem, stream>>>((const TI*)e, st, row_first, n_block_rows, bs, bs_log2, (__nv_bfloat16*)out);
+            break;
+        case BSP_F32:
+            softmax_normalize_kernel<TI, float><<<grid, 256, smem, stream>>>((const TI*)e, st, row_first, n_block_rows, bs, bs_log2, (float*)out);
+            break;
+        default: return BSP_ERR_UNSUPPORTED;
+    }
+    BSP_LAUNCH_CHECK();
+    return BSP_OK;
+}
+
 // Warps per CTA: enough matrix rows of a block in flight together that HBM sees kilobytes of each
 // block at a time (measured: 32 warps for block size >= 64, fewer for the short rows of small blocks).
 static int list_warps(int bs) {
@@ -287,4 +382,21 @@ extern "C" int bsp_softmax_bwd(const float* grad_out, const float* o, int64_t n_
     }
     BSP_LAUNCH_CHECK();
     return BSP_OK;
+}
+
+extern "C" int bsp_softmax_normalize(const void* e, int in_dtype, const float* stats, int64_t n_blocks,
+                                     const int32_t* row_first, int64_t n_block_rows, int bs, void* out,
+                                     int out_dtype, void* stream_) {
+    if (n_blocks < 0 || n_block_rows < 0 || bs < 16 || (bs & (bs - 1)) || bs > 4096) return BSP_ERR_INVALID_ARG;
+    if (n_blocks == 0 || n_block_rows == 0) return BSP_OK;
+    if (!e || !stats || !row_first || !out) return BSP_ERR_INVALID_ARG;
+    if (n_blocks > INT32_MAX) return BSP_ERR_UNSUPPORTED;
+    if (((uintptr_t)e | (uintptr_t)out) & 15 || ((uintptr_t)stats & 7)) return BSP_ERR_INVALID_ARG;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    switch (in_dtype) {
+        case BSP_F16: return launch_normalize_out<__half>(out_dtype, e, stats, row_first, n_block_rows, bs, out, stream);
+        case BSP_BF16: return launch_normalize_out<__nv_bfloat16>(out_dtype, e, stats, row_first, n_block_rows, bs, out, stream);
+        case BSP_F32: return launch_normalize_out<float>(out_dtype, e, stats, row_first, n_block_rows, bs, out, stream);
+        default: return BSP_ERR_UNSUPPORTED;
+    }
 }
