@@ -347,6 +347,38 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(s)}
 
 
+def bind_to_gpu_numa_node(index: int) -> dict:
+    """Best effort: restricts this process to the CPUs of the NUMA node the GPU hangs off, so that the
+    pinned host buffers of the end-to-end leg (allocated afterwards, first touch) are local to it.
+    Returns what was found and done; never raises."""
+    info = {"bound": False}
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(index)).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        dom, rest = bus.split(":", 1)
+        path = f"/sys/bus/pci/devices/{dom[-4:].lower()}:{rest.lower()}/numa_node"
+        with open(path) as f:
+            node = int(f.read().strip())
+        nodes = [d for d in os.listdir("/sys/devices/system/node") if d.startswith("node") and d[4:].isdigit()]
+        info.update({"gpu_numa_node": node, "host_numa_nodes": len(nodes)})
+        if node >= 0 and len(nodes) > 1:
+            with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+                cpus = set()
+                for part in f.read().strip().split(","):
+                    lo, _, hi = part.partition("-")
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+            allowed = cpus & os.sched_getaffinity(0)
+            if allowed:
+                os.sched_setaffinity(0, allowed)
+                info["bound"] = True
+                info["cpus"] = len(allowed)
+    except Exception as exc:
+        info["note"] = repr(exc)[:120]
+    return info
+
+
 def physical_gpu_index(local_index: int) -> int:
     vis = os.environ.get("CUDA_VISIBLE_DEVICES")
     if vis:
@@ -662,6 +694,60 @@ def sub_record(name, dev, args, peaks):
     return rec, prob
 
 
+def attention_chain_record(dev, peaks, batch=None):
+    """Attention by parts at the size of the config3 -> config4 pair: P = softmax(scale * Q K^T) on the
+    banded causal layout in bf16, then O = P V.  Times the part between the operands and P once as the
+    chain of separate ops (matmul -> scale and cast to fp32 -> softmax -> cast to bf16) and once as the
+    fused op (softmax in the matmul's epilogue plus one normalising pass), and the P V product."""
+    import blksprs_b200 as bs
+    lq, lkt, lo, bsz, dtype = workload_layouts("config3", batch=batch)
+    q, kt, _ = workload_values("config3", lq, lkt, lo, bsz, dtype, seed=0, device=dev)
+    B = lq.size(0)
+    lv = torch.ones((B, 64, 2), dtype=torch.bool)
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    v = torch.randn((int(lv.sum()), bsz, bsz), generator=g, device=dev).to(torch.bfloat16)
+    lqd, lktd, lod, lvd = lq.to(dev), lkt.to(dev), lo.to(dev), lv.to(dev)
+    scale = 128 ** -0.5
+    caches = [{}, {}, {}]
+
+    def chain():
+        scores = bs.ops.matmul(q, lqd, kt, lktd, lod, bsz, caches[0])
+        return bs.ops.softmax(scores.float() * scale, lod, bsz, layout_cache=caches[1]).to(torch.bfloat16)
+
+    def fused():
+        return bs.ops.matmul_softmax(q, lqd, kt, lktd, lod, bsz, scale=scale, out_dtype=torch.bfloat16,
+                                     layout_cache=caches[0])
+
+    def pv(p):
+        return bs.ops.matmul(p, lod, v, lvd, lvd, bsz, caches[2])
+
+    def timed(fn, n=5):
+        for _ in range(2):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    p_chain, p_fused = chain(), fused()
+    diff = float((p_chain.float() - p_fused.float()).abs().max()) / max(float(p_chain.float().abs().max()), 1e-30)
+    t_chain, t_fused = timed(chain), timed(fused)
+    t_pv = timed(lambda: pv(p_fused))
+    n_el = int(lo.sum()) * bsz * bsz
+    return {
+        "batch": B, "score_elements": n_el, "scores_to_probabilities_ms": {"separate_ops": t_chain, "fused": t_fused},
+        "pv_ms": t_pv, "chain_ms": {"separate_ops": t_chain + t_pv, "fused": t_fused + t_pv},
+        "bytes_moved_model": {"separate_ops": n_el * (2 + 2 + 4 + 4 + 4 + 4 + 2), "fused": n_el * (2 + 2 + 2),
+                              "what": "score-sized tensors written and read between the matmul's accumulators and P"},
+        "max_rel_diff_fused_vs_separate": diff,
+    }
+
+
 def run_gpu_arm(args):
     import torch.distributed as dist
     import blksprs_b200 as bs
@@ -673,6 +759,7 @@ def run_gpu_arm(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    numa = bind_to_gpu_numa_node(physical_gpu_index(local))
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     name = args.config
@@ -799,6 +886,7 @@ def run_gpu_arm(args):
             "api": {"ms_per_step": api_ms, "tflops": flops_all / (api_ms * 1e-3) / 1e12 if api_ms else None,
                     "what": "ops.matmul (+ backward) on device tensors, warm layout cache, validation on"},
             "gpu_launches": prob.launches_per_step * args.steps * R,
+            "host": {"numa": numa, "cpus": os.cpu_count()},
             "clocks": clocks.summary(),
         }
         if prob.forward_only:
@@ -873,6 +961,11 @@ def run_gpu_arm(args):
             triton_rec["what"] = ("reference bs.ops.matmul (Triton, BLKSPRS_AUTOTUNE=DEFAULT, autotune excluded) on the "
                                   "same GPU and tensors, warm layout_cache; speedup = reference validation_off time "
                                   "/ ours (kernel only, and through the public op with validation on)")
+        try:
+            also["attention_chain"] = attention_chain_record(dev, peaks)
+        except Exception as exc:
+            also["attention_chain"] = {"error": repr(exc)[:300]}
+        torch.cuda.empty_cache()
         line["also"] = also
         line["triton_reference"] = triton_rec
         if not args.no_cpu_baseline:

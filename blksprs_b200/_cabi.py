@@ -58,6 +58,11 @@ SIGNATURES = {
                                 c_void_p, c_int64,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_int, c_int, c_int,
                                 c_int, c_void_p, c_void_p]),
+    "bsp_matmul_umma_softmax": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, ctypes.c_float,
+                                        c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
+                                        c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "bsp_softmax_normalize": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_int,
+                                      c_void_p]),
     "bsp_to_sparse": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "bsp_to_dense": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, ctypes.c_uint64,
                              c_void_p, c_void_p]),

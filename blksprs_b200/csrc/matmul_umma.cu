@@ -36,6 +36,8 @@
 // Every wait is bounded (about one second): a wait that runs out records
 // BSP_ERR_DEVICE_TIMEOUT in the status word, all roles leave their loops, outstanding copies
 // and MMAs are drained with bounded waits, tensor memory is freed and the kernel returns.
+#include <float.h>
+
 #include <atomic>
 
 #include "common.cuh"
@@ -51,31 +53,11 @@ constexpr uint32_t kCtrlLast = 0x100u;
 // Slots of the per-CTA queue of unit numbers (dynamic scheduling).
 constexpr int kUnitQueue = 8;
 
-#ifdef BSP_UMMA_PROFILE
-// Debug build only: per-CTA cycle counters (8 per CTA) read back by bsp_debug_read_prof.
-__device__ long long g_prof[1024 * 8];
-#define PROF_DECL(name) long long name = 0
-#define PROF_T0(t) long long t = clock64()
-#define PROF_ADD(acc, t) acc += clock64() - t
-#define PROF_STORE(i, v) g_prof[blockIdx.x * 8 + (i)] = (v)
-#else
-#define PROF_DECL(name)
-#define PROF_T0(t)
-#define PROF_ADD(acc, t)
-#define PROF_STORE(i, v)
-#endif
-
 // Per (block size, panel width): ring depth, accumulator groups (of G x bs tensor-memory
 // columns each) and resident CTAs per SM.  Shared memory: stages x (1 + G) x bs x 128 bytes.
 template <int BS, int G> struct PCfg;
-#ifndef BSP_C641_STAGES
-#define BSP_C641_STAGES 4
-#define BSP_C641_GROUPS 2
-#define BSP_C641_CTAS 3
-#endif
 template <> struct PCfg<64, 1> {   // 3 x (4 x 16 KiB), 3 x 128 columns
-    static constexpr int kStages = BSP_C641_STAGES, kGroups = BSP_C641_GROUPS, kCtasPerSm = BSP_C641_CTAS,
-                         kThreads = 32 * (kStages + 5);
+    static constexpr int kStages = 4, kGroups = 2, kCtasPerSm = 3, kThreads = 32 * (kStages + 5);
 };
 template <> struct PCfg<64, 2> {   // 2 x (4 x 24 KiB), 2 x 256 columns
     static constexpr int kStages = 4, kGroups = 2, kCtasPerSm = 2, kThreads = 32 * (kStages + 5);
@@ -123,6 +105,21 @@ __device__ __forceinline__ void tc_mma_elect(uint32_t d_tmem, uint64_t adesc, ui
     else tc_mma_f16_elect(d_tmem, adesc, bdesc, idesc, accumulate);
 }
 
+// Softmax epilogue, block size 128 (lane = accumulator row): the maximum of scale * x over the row's
+// 128 columns, read from tensor memory ahead of the pass that exponentiates.
+__device__ __forceinline__ float row_max_scaled(uint32_t taddr, float scale) {
+    float m = -FLT_MAX;
+#pragma unroll
+    for (int c0 = 0; c0 < 128; c0 += 32) {
+        uint32_t v[32];
+        tc_ld32(taddr + c0, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) m = fmaxf(m, __uint_as_float(v[e]) * scale);
+    }
+    return m;
+}
+
 // Exchange inside a quad (lanes 4r .. 4r + 3).  In: thread q holds words w[g], g = 0..7, where word (g, q)
 // lies at byte 16 g + 4 q of a 128-byte row.  Out: thread q holds the eight words of bytes
 // [32 q, 32 q + 32): the word at byte 32 q + 4 j is in slot {0, 2, 4, 6, 1, 3, 5, 7}[j].  Two butterfly
@@ -164,11 +161,17 @@ __device__ __forceinline__ void octet_gather_chunks(uint32_t (&w)[32], int lane)
     }
 }
 
-template <typename T, int BS, int OP, int G, bool BIAS>
+// What the epilogue does besides converting and storing the accumulators.
+constexpr int kEpiPlain = 0;    // nothing
+constexpr int kEpiBias = 1;     // adds the bias row of the block's column (the linear helper)
+constexpr int kEpiSoftmax = 2;  // scaled scores -> exp(s - row maximum inside the block), plus (maximum, sum) per row
+
+template <typename T, int BS, int OP, int G, int EPI>
 __global__ void __launch_bounds__(PCfg<BS, G>::kThreads, PCfg<BS, G>::kCtasPerSm)
 matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    int64_t n_a, int64_t n_b, T* __restrict__ out,
                    const T* __restrict__ bias, const int64_t* __restrict__ out_lut,
+                   float scale, float2* __restrict__ stats,
                    const int32_t* __restrict__ panel_first, const int32_t* __restrict__ step_off,
                    const int32_t* __restrict__ steps, const int32_t* __restrict__ touched,
                    const int32_t* __restrict__ unit_panel, const int32_t* __restrict__ unit_step,
@@ -182,6 +185,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     constexpr int S = C::kStages, NG = C::kGroups, H = BS / KE, KC = BS / KE;
     constexpr bool A_MN = (OP == BSP_OP_TN);
     constexpr bool B_MN = (OP != BSP_OP_NT);
+    constexpr bool BIAS = EPI == kEpiBias, SOFTMAX = EPI == kEpiSoftmax;
     constexpr int TMEM_COLS = tmem_cols_pow2(NG * G * BS);
     static_assert(S <= 32 && G <= 4 && G * BS <= 256, "panel configuration out of range");
 
@@ -344,8 +348,6 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 int4 c0 = make_int4(0, 0, 0, 0), c1 = c0, n0 = c0, n1 = c0;
                 bool have = false;         // (c0, c1) is the record of this lane's next entry
                 uint32_t uses = 0;         // how often this lane's stage has been filled
-                PROF_DECL(w_empty);
-                PROF_T0(t_start);
                 while (u >= 0 && alive) {
                     auto peek_next = [&]() {
                         if (nu == -2) {
@@ -390,10 +392,8 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         const uint32_t sa = data + slot * L::kStageBytes;
                         const uint32_t sb = sa + L::kChunkBytes;
                         unsigned long long t0 = 0;
-                        PROF_T0(tw);
                         for (uint32_t spins = 1;; ++spins) {
                             if (mbar_try_wait(ebar, phase ^ 1u)) {
-                                PROF_ADD(w_empty, tw);
                                 // first-touch flags count for the step's first chunk only; the panel ends
                                 // with the step's last chunk
                                 ctrl_slot[slot] = (ctrl & (kc == 0 ? ~0u : ~0xF0u)) & (kc == KC - 1 ? ~0u : ~kCtrlLast);
@@ -459,10 +459,6 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     nu = -2;
                     ++n;
                 }
-                if (slot == 0) {
-                    PROF_STORE(0, clock64() - t_start);
-                    PROF_STORE(1, w_empty);
-                }
             }
         } else if (warp == S) {
             // ---------------- MMA issuer ----------------
@@ -474,11 +470,6 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 uint32_t stage_parity = 0;  // bit s = parity of the next fill of stage s
                 uint32_t grp_phase = 0;
                 bool new_panel = true, alive = true;
-                PROF_DECL(w_full);
-                PROF_DECL(w_tempty);
-                PROF_DECL(w_issue);
-                PROF_DECL(w_commit);
-                PROF_T0(t_start);
                 auto entries_of = [&](int uu) { return uu >= 0 ? (unit_step[uu + 1] - unit_step[uu]) * KC : 0; };
                 int n = 0;  // position in this CTA's unit sequence
                 int u = unit_at(0, true);
@@ -489,15 +480,10 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     int next_entries = entries_of(nu);
                     for (int e = 0; e < n_entries; ++e) {
                         if (new_panel) {
-                            PROF_T0(tw);
                             if (!mbar_wait(tempty_bar + 8 * grp, grp_phase ^ 1u, abort_flag, status_word)) { alive = false; break; }
-                            PROF_ADD(w_tempty, tw);
                         }
-                        PROF_T0(tw2);
                         if (!mbar_wait(full_bar + 8 * stage, (stage_parity >> stage) & 1u, abort_flag, status_word)) { alive = false; break; }
-                        PROF_ADD(w_full, tw2);
                         stage_parity ^= 1u << stage;
-                        PROF_T0(t_a);
                         tc_fence_after();
                         const uint32_t ctrl = ctrl_slot[stage];
                         const uint32_t present = ctrl & 0xFu, first = (ctrl >> 4) & 0xFu;
@@ -533,10 +519,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 }
                             }
                         }
-                        PROF_ADD(w_issue, t_a);
-                        PROF_T0(t_b);
                         tc_commit_elect(empty_bar + 8 * stage);
-                        PROF_ADD(w_commit, t_b);
                         new_panel = false;
                         if (ctrl & kCtrlLast) {
                             tc_commit_elect(tfull_bar + 8 * grp);
@@ -554,11 +537,6 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     n_entries = next_entries;
                     ++n;
                 }
-                if (lane == 0) PROF_STORE(2, clock64() - t_start);
-                if (lane == 0) PROF_STORE(3, w_full);
-                if (lane == 0) PROF_STORE(4, w_tempty);
-                if (lane == 0) PROF_STORE(5, w_issue);
-                if (lane == 0) PROF_STORE(6, w_commit);
                 // every MMA issued so far has to complete before tensor memory may be freed; this wait has
                 // its own limit and does not give up early because another role has aborted
                 tc_commit_elect(drain_bar);
@@ -573,20 +551,25 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             int grp = 0;
             uint32_t grp_phase = 0;
             bool alive = true;
-            PROF_DECL(w_tfull);
-            PROF_T0(t_start);
             // the bias row of output block p (nullptr without a bias): bias[column block * BS ...]
             auto bias_of = [&](int p) -> const T* {
                 if constexpr (!BIAS) return nullptr;
                 return bias + out_lut[(int64_t)p * 3 + 2] * BS;
             };
-            // a block nothing was accumulated into: zeros, or the bias row repeated
-            auto zero_quarter = [&](T* o, const T* brow) {
+            // a block nothing was accumulated into: zeros, or the bias row repeated; in softmax mode its
+            // scores are all zero, so exp(s - maximum) = 1 everywhere, maximum 0, sum BS
+            auto zero_quarter = [&](T* o, const T* brow, int p) {
                 uint4* dst = reinterpret_cast<uint4*>(o + (int64_t)wq * ROWS_PER_WARP * BS);
                 constexpr int VECS = ROWS_PER_WARP * BS * (int)sizeof(T) / 16, ROW_VECS = BS * (int)sizeof(T) / 16;
                 if (BIAS && brow) {
                     const uint4* bv = reinterpret_cast<const uint4*>(brow);
                     for (int i = lane; i < VECS; i += 32) dst[i] = __ldg(bv + i % ROW_VECS);
+                } else if (SOFTMAX) {
+                    uint32_t one;
+                    if constexpr (sizeof(T) == 4) one = __float_as_uint(1.0f);
+                    else one = pack2<T>(1.0f, 1.0f);
+                    for (int i = lane; i < VECS; i += 32) dst[i] = make_uint4(one, one, one, one);
+                    if (row_valid) stats[(int64_t)p * BS + row] = make_float2(0.f, (float)BS);
                 } else {
                     for (int i = lane; i < VECS; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
                 }
@@ -637,12 +620,10 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         const int tmask = __shfl_sync(0xffffffffu, my_touched, j);
                         if (nsteps == 0) {
                             for (int q = 0; q < g; ++q)
-                                zero_quarter(out + (int64_t)(first + q) * BS * BS, bias_of(first + q));
+                                zero_quarter(out + (int64_t)(first + q) * BS * BS, bias_of(first + q), first + q);
                             continue;
                         }
-                        PROF_T0(tw);
                         if (!mbar_wait(tfull_bar + 8 * grp, grp_phase, abort_flag, status_word)) alive = false;
-                        PROF_ADD(w_tfull, tw);
                         alive = __all_sync(0xffffffffu, alive);
                         if (!alive) break;
                         tc_fence_after();
@@ -650,7 +631,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             T* o = out + (int64_t)(first + q) * BS * BS;
                             const T* brow = bias_of(first + q);
                             if (!((tmask >> q) & 1)) {
-                                zero_quarter(o, brow);
+                                zero_quarter(o, brow, first + q);
                                 continue;
                             }
                             const uint32_t taddr = tmem_base + grp * (G * BS) + q * BS + ((uint32_t)(wq * 32) << 16);
@@ -670,6 +651,42 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                         v[4 * gq + 1] = __float_as_uint(__uint_as_float(v[4 * gq + 1]) + b1);
                                         v[4 * gq + 2] = __float_as_uint(__uint_as_float(v[4 * gq + 2]) + b0);
                                         v[4 * gq + 3] = __float_as_uint(__uint_as_float(v[4 * gq + 3]) + b1);
+                                    }
+                                }
+                                if constexpr (SOFTMAX) {
+                                    // rows r0 (v[4g], v[4g+1]) and r0 + 8 (v[4g+2], v[4g+3]); a row's 64 columns
+                                    // are spread over the four threads of a quad
+                                    float ma = -FLT_MAX, mb = -FLT_MAX;
+#pragma unroll
+                                    for (int gq = 0; gq < 8; ++gq) {
+#pragma unroll
+                                        for (int e = 0; e < 4; ++e) v[4 * gq + e] = __float_as_uint(__uint_as_float(v[4 * gq + e]) * scale);
+                                        ma = fmaxf(ma, fmaxf(__uint_as_float(v[4 * gq]), __uint_as_float(v[4 * gq + 1])));
+                                        mb = fmaxf(mb, fmaxf(__uint_as_float(v[4 * gq + 2]), __uint_as_float(v[4 * gq + 3])));
+                                    }
+                                    ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, 1));
+                                    mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 1));
+                                    ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, 2));
+                                    mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 2));
+                                    float la = 0.f, lb = 0.f;
+#pragma unroll
+                                    for (int gq = 0; gq < 8; ++gq) {
+                                        const float a0 = __expf(__uint_as_float(v[4 * gq]) - ma), a1 = __expf(__uint_as_float(v[4 * gq + 1]) - ma);
+                                        const float b0 = __expf(__uint_as_float(v[4 * gq + 2]) - mb), b1 = __expf(__uint_as_float(v[4 * gq + 3]) - mb);
+                                        la += a0 + a1;
+                                        lb += b0 + b1;
+                                        v[4 * gq] = __float_as_uint(a0);
+                                        v[4 * gq + 1] = __float_as_uint(a1);
+                                        v[4 * gq + 2] = __float_as_uint(b0);
+                                        v[4 * gq + 3] = __float_as_uint(b1);
+                                    }
+                                    la += __shfl_xor_sync(0xffffffffu, la, 1);
+                                    lb += __shfl_xor_sync(0xffffffffu, lb, 1);
+                                    la += __shfl_xor_sync(0xffffffffu, la, 2);
+                                    lb += __shfl_xor_sync(0xffffffffu, lb, 2);
+                                    if (qd == 0) {
+                                        stats[(int64_t)(first + q) * BS + r0] = make_float2(ma, la);
+                                        stats[(int64_t)(first + q) * BS + r0 + 8] = make_float2(mb, lb);
                                     }
                                 }
                                 T* d0 = o + (int64_t)r0 * BS;
@@ -711,12 +728,22 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 // the same chunk of the group's 8 rows, so that 8 neighbouring lanes store one
                                 // row's whole 128-byte line per instruction.
                                 T* obase = o + (int64_t)(wq * 32 + (lane & ~7)) * BS + (lane & 7) * 8;
+                                float rmax = -FLT_MAX, rsum = 0.f;  // softmax mode: this lane's row
+                                if constexpr (SOFTMAX) rmax = row_max_scaled(taddr, scale);
 #pragma unroll
                                 for (int half = 0; half < 2; ++half) {
                                     uint32_t v[64];
                                     tc_ld32(taddr + half * 64, v);
                                     tc_ld32(taddr + half * 64 + 32, v + 32);
                                     tc_wait_ld();
+                                    if constexpr (SOFTMAX) {
+#pragma unroll
+                                        for (int e = 0; e < 64; ++e) {
+                                            const float ex = __expf(__uint_as_float(v[e]) * scale - rmax);
+                                            rsum += ex;
+                                            v[e] = __float_as_uint(ex);
+                                        }
+                                    }
                                     if (BIAS && brow) {
                                         const uint4* bv = reinterpret_cast<const uint4*>(brow + half * 64);
 #pragma unroll
@@ -737,7 +764,10 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                     for (int i = 0; i < 8; ++i)
                                         st_global_16B(obase + (int64_t)i * BS + half * 64, w + 4 * i);
                                 }
+                                if constexpr (SOFTMAX) stats[(int64_t)(first + q) * BS + row] = make_float2(rmax, rsum);
                             } else {
+                            float rmax = -FLT_MAX, rsum = 0.f;  // softmax mode: this lane's row
+                            if constexpr (SOFTMAX && BS == 128) rmax = row_max_scaled(taddr, scale);
 #pragma unroll
                             for (int c0 = 0; c0 < BS; c0 += 32) {
                                 uint32_t v[32];
@@ -756,6 +786,14 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                             v[EPV * i + e] = __float_as_uint(__uint_as_float(v[EPV * i + e]) + (float)be[e]);
                                     }
                                 }
+                                if constexpr (SOFTMAX) {
+#pragma unroll
+                                    for (int e = 0; e < 32; ++e) {
+                                        const float ex = __expf(__uint_as_float(v[e]) * scale - rmax);
+                                        rsum += ex;
+                                        v[e] = __float_as_uint(ex);
+                                    }
+                                }
                                 if (row_valid) {
                                     // 32 fp32 columns = 128 bytes of the row: four 32-byte stores
                                     T* dst = o + (int64_t)row * BS + c0;
@@ -770,7 +808,10 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                     }
                                 }
                             }
-                                                    }
+                            if constexpr (SOFTMAX) {
+                                if (row_valid) stats[(int64_t)(first + q) * BS + row] = make_float2(rmax, rsum);
+                            }
+                            }
                         }
                         tc_fence_before();
                         __syncwarp();
@@ -800,7 +841,6 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 meta_ok = nmeta_ok;
                 ++n;
             }
-            if (warp == S + 1 && lane == 0) PROF_STORE(7, w_tfull);
         }
     }
 
@@ -835,12 +875,12 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
 }
 
-template <typename T, int BS, int OP, int G, bool BIAS>
+template <typename T, int BS, int OP, int G, int EPI>
 int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_t n_b, void* out,
-               const void* bias, const int64_t* out_lut, const int32_t* panel_first, const int32_t* step_off, const int32_t* steps,
+               const void* bias, const int64_t* out_lut, float scale, float* stats, const int32_t* panel_first, const int32_t* step_off, const int32_t* steps,
                const int32_t* touched, const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units,
                int32_t* sched, int dtype, int32_t* status_word, cudaStream_t stream) {
-    auto kern = matmul_umma_kernel<T, BS, OP, G, BIAS>;
+    auto kern = matmul_umma_kernel<T, BS, OP, G, EPI>;
     constexpr int smem = PSmem<BS, G>::kTotal;
     // the shared-memory opt-in is a per-device property of this instantiation: set it once per device
     static std::atomic<uint64_t> opted_in{0};
@@ -864,32 +904,38 @@ int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    BSP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, n_a, n_b, (T*)out, (const T*)bias, out_lut, panel_first, step_off,
+    BSP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, n_a, n_b, (T*)out, (const T*)bias, out_lut, scale,
+                                    reinterpret_cast<float2*>(stats), panel_first, step_off,
                                     steps, touched, unit_panel, unit_step, (int)n_units, idesc_no_n, sched, status_word));
     return BSP_OK;
 }
 
-#define BSP_LAUNCH_ARGS ma, mb, n_a, n_b, out, bias, out_lut, panel_first, step_off, steps, touched, unit_panel, unit_step, n_units, sched, dtype, status_word, stream
+#define BSP_LAUNCH_ARGS ma, mb, n_a, n_b, out, bias, out_lut, scale, stats, panel_first, step_off, steps, touched, unit_panel, unit_step, n_units, sched, dtype, status_word, stream
 
 template <typename T, int BS, int G>
 int launch_op(int op, const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_t n_b, void* out,
-              const void* bias, const int64_t* out_lut, const int32_t* panel_first, const int32_t* step_off, const int32_t* steps, const int32_t* touched,
+              const void* bias, const int64_t* out_lut, float scale, float* stats, const int32_t* panel_first, const int32_t* step_off, const int32_t* steps, const int32_t* touched,
               const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units, int32_t* sched, int dtype,
               int32_t* status_word, cudaStream_t stream) {
     switch (op) {
-        // a bias is added by the forward product only
+        // a bias or the softmax epilogue goes with the forward product only
         case BSP_OP_NN:
-            return bias ? launch_cfg<T, BS, BSP_OP_NN, G, true>(BSP_LAUNCH_ARGS)
-                        : launch_cfg<T, BS, BSP_OP_NN, G, false>(BSP_LAUNCH_ARGS);
-        case BSP_OP_NT: return bias ? BSP_ERR_UNSUPPORTED : launch_cfg<T, BS, BSP_OP_NT, G, false>(BSP_LAUNCH_ARGS);
-        case BSP_OP_TN: return bias ? BSP_ERR_UNSUPPORTED : launch_cfg<T, BS, BSP_OP_TN, G, false>(BSP_LAUNCH_ARGS);
+            if (bias && stats) return BSP_ERR_UNSUPPORTED;
+            if (stats) return launch_cfg<T, BS, BSP_OP_NN, G, kEpiSoftmax>(BSP_LAUNCH_ARGS);
+            return bias ? launch_cfg<T, BS, BSP_OP_NN, G, kEpiBias>(BSP_LAUNCH_ARGS)
+                        : launch_cfg<T, BS, BSP_OP_NN, G, kEpiPlain>(BSP_LAUNCH_ARGS);
+        case BSP_OP_NT:
+            return (bias || stats) ? BSP_ERR_UNSUPPORTED : launch_cfg<T, BS, BSP_OP_NT, G, kEpiPlain>(BSP_LAUNCH_ARGS);
+        case BSP_OP_TN:
+            return (bias || stats) ? BSP_ERR_UNSUPPORTED : launch_cfg<T, BS, BSP_OP_TN, G, kEpiPlain>(BSP_LAUNCH_ARGS);
         default: return BSP_ERR_INVALID_ARG;
     }
 }
 
 template <typename T>
 int launch_shape(int bs, int width, int op, const CUtensorMap& ma, const CUtensorMap& mb, int64_t n_a, int64_t n_b,
-                 void* out, const void* bias, const int64_t* out_lut, const int32_t* panel_first,
+                 void* out, const void* bias, const int64_t* out_lut, float scale, float* stats,
+                 const int32_t* panel_first,
                  const int32_t* step_off, const int32_t* steps,
                  const int32_t* touched, const int32_t* unit_panel, const int32_t* unit_step, int32_t n_units,
                  int32_t* sched, int dtype, int32_t* status_word, cudaStream_t stream) {
@@ -916,11 +962,6 @@ __global__ void wait_limit_selftest_kernel(unsigned long long limit_ns, int32_t*
 
 }  // namespace
 
-#ifdef BSP_UMMA_PROFILE
-extern "C" int bsp_debug_read_prof(long long* host_out, int n) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_prof, sizeof(long long) * n);
-}
-#endif
 
 bool umma_applicable(int dtype, int bs) {
     return (dtype == BSP_F16 || dtype == BSP_BF16 || dtype == BSP_F32) && (bs == 64 || bs == 128);
@@ -948,11 +989,12 @@ extern "C" int bsp_umma_num_ctas(int dtype, int bs, int width) {
     return umma::num_sms() * per_sm;
 }
 
-extern "C" int bsp_matmul_umma(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out, int64_t n_out,
-                               const void* bias, const int64_t* out_lut, const int32_t* panel_first, int64_t n_panels, const int32_t* step_off,
-                               const int32_t* steps, const int32_t* touched, const int32_t* unit_panel,
-                               const int32_t* unit_step, int32_t n_units, int32_t* sched, int width, int bs,
-                               int dtype, int op, int32_t* status_word, void* stream_) {
+static int matmul_umma_common(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out, int64_t n_out,
+                              const void* bias, const int64_t* out_lut, float scale, float* stats,
+                              const int32_t* panel_first, int64_t n_panels, const int32_t* step_off,
+                              const int32_t* steps, const int32_t* touched, const int32_t* unit_panel,
+                              const int32_t* unit_step, int32_t n_units, int32_t* sched, int width, int bs,
+                              int dtype, int op, int32_t* status_word, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     if (n_a < 1 || n_b < 1 || n_out < 0 || n_panels < 0) return BSP_ERR_INVALID_ARG;
     if (!umma_applicable(dtype, bs) || (width != 1 && width != 2)) return BSP_ERR_UNSUPPORTED;
@@ -961,11 +1003,14 @@ extern "C" int bsp_matmul_umma(const void* a, int64_t n_a, const void* b, int64_
     if (!a || !b || !out || !panel_first || !step_off || !steps || !touched || !unit_panel || !unit_step ||
         n_units < 1)
         return BSP_ERR_INVALID_ARG;
+    // Block rows are the second coordinate of the operands' 2-D tensor maps (32-bit).  At 8 KiB per
+    // 64-block of 16-bit data the limit is 33.5 million blocks = 275 GB per operand, beyond the device.
     if (n_a * bs > 0x7fffffffLL || n_b * bs > 0x7fffffffLL || n_out > 0x7fffffffLL) return BSP_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) ||
         (reinterpret_cast<uintptr_t>(out) & 31) || (reinterpret_cast<uintptr_t>(steps) & 15))
         return BSP_ERR_INVALID_ARG;
     if (bias && (!out_lut || (reinterpret_cast<uintptr_t>(bias) & 15))) return BSP_ERR_INVALID_ARG;
+    if (stats && (reinterpret_cast<uintptr_t>(stats) & 7)) return BSP_ERR_INVALID_ARG;
     CUtensorMap ma, mb;
     // a block read MN-major is fetched 64 rows at a time, one read K-major as bs rows x 64 columns
     int st = umma::make_block_map(&ma, a, n_a, bs, dtype, op == BSP_OP_TN);
@@ -975,4 +1020,26 @@ extern "C" int bsp_matmul_umma(const void* a, int64_t n_a, const void* b, int64_
     if (dtype == BSP_F32) return launch_shape<float>(bs, width, op, BSP_LAUNCH_ARGS);
     if (dtype == BSP_F16) return launch_shape<__half>(bs, width, op, BSP_LAUNCH_ARGS);
     return launch_shape<__nv_bfloat16>(bs, width, op, BSP_LAUNCH_ARGS);
+}
+
+extern "C" int bsp_matmul_umma(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out, int64_t n_out,
+                               const void* bias, const int64_t* out_lut, const int32_t* panel_first, int64_t n_panels, const int32_t* step_off,
+                               const int32_t* steps, const int32_t* touched, const int32_t* unit_panel,
+                               const int32_t* unit_step, int32_t n_units, int32_t* sched, int width, int bs,
+                               int dtype, int op, int32_t* status_word, void* stream_) {
+    return matmul_umma_common(a, n_a, b, n_b, out, n_out, bias, out_lut, 1.0f, nullptr, panel_first, n_panels, step_off,
+                              steps, touched, unit_panel, unit_step, n_units, sched, width, bs, dtype, op, status_word,
+                              stream_);
+}
+
+extern "C" int bsp_matmul_umma_softmax(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
+                                       int64_t n_out, float* stats, float scale, const int32_t* panel_first,
+                                       int64_t n_panels, const int32_t* step_off, const int32_t* steps,
+                                       const int32_t* touched, const int32_t* unit_panel, const int32_t* unit_step,
+                                       int32_t n_units, int32_t* sched, int width, int bs, int dtype,
+                                       int32_t* status_word, void* stream_) {
+    if (n_out > 0 && !stats) return BSP_ERR_INVALID_ARG;
+    return matmul_umma_common(a, n_a, b, n_b, out, n_out, nullptr, nullptr, scale, stats, panel_first, n_panels,
+                              step_off, steps, touched, unit_panel, unit_step, n_units, sched, width, bs, dtype,
+                              BSP_OP_NN, status_word, stream_);
 }

@@ -31,8 +31,8 @@ from . import _cabi
 BLOCK_COST = 1
 # A unit should hold about this much work (pairs + blocks): large enough to amortise the ring
 # restart at a unit boundary, small enough that concurrently processed units share operands in L2.
-UNIT_COST = int(os.environ.get("BLKSPRS_B200_UNIT_COST", "48"))
-MAX_UNITS_PER_CTA = int(os.environ.get("BLKSPRS_B200_MAX_UNITS", "64"))
+UNIT_COST = 48
+MAX_UNITS_PER_CTA = 64
 # With the dynamic schedule a unit is the grain of load balancing: small, but large enough that
 # drawing it from the counter stays invisible.  Measured optimum per block size (a pair of 128-blocks
 # is eight times the work of a pair of 64-blocks).
@@ -53,7 +53,7 @@ _kernel_choice = os.environ.get("BLKSPRS_B200_KERNEL", "auto")
 # this ratio (0.5 = every step serves two (A, B) pairs).  Measured on B200: dense-B products (P*V,
 # dO*V^T on an attention layout, sparse x dense at block size 128) gain 1.15-1.35x, random x random
 # layouts (ratio ~0.85) lose.
-PANEL_STEP_RATIO = float(os.environ.get("BLKSPRS_B200_PANEL_RATIO", "0.58"))
+PANEL_STEP_RATIO = 0.58
 PANEL_AUTO_BLOCK_SIZES = (64, 128)
 
 
@@ -227,7 +227,7 @@ def build_step_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor
         # static round-robin: a unit is several times the heaviest panel, so that indivisible
         # panels cannot unbalance the CTAs; dynamic hand-out needs no such margin
         if SCHEDULE == "dynamic":
-            target = int(os.environ.get("BLKSPRS_B200_UNIT_COST", UNIT_COST_DYNAMIC.get(bs, 24)))
+            target = UNIT_COST_DYNAMIC.get(bs, 24)
             # a whole number of units per CTA: equally fast CTAs then finish together
             # no floor at the heaviest panel: a panel heavier than a unit just leaves a few units empty,
             # while larger units would widen the window of output the CTAs work in beyond what L2 holds

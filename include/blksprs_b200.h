@@ -325,6 +325,34 @@ int bsp_softmax_fwd(const float* x, int64_t n_x, const int64_t* packed,
 int bsp_softmax_bwd(const float* grad_out, const float* o, int64_t n_x, const int64_t* packed,
                     int64_t B, int64_t R, int64_t C, int bs, float* grad_x, void* stream);
 
+/* Matmul + scale + softmax, first half: the forward product of bsp_matmul_umma
+ * (same plan arguments, BSP_OP_NN) whose epilogue turns the fp32 accumulators
+ * into s = scale * acc, takes the maximum m of every matrix row inside the
+ * block, and writes exp(s - m) to `out` (dtype of the operands) and
+ * (m, sum of exp) to stats[block][row] (fp32 pairs, (n_out, bs, 2)).  Blocks
+ * without a pair hold scores of zero: exp = 1, stats (0, bs).  Together with
+ * bsp_softmax_normalize this replaces the chain matmul -> multiply by a scale
+ * -> softmax of the reference (blksprs/ops/matmul.py:17-67,
+ * blksprs/ops/softmax.py:23-144, as used in test/cases/test_blocksparse.py:
+ * 1517-1529) without the score tensor ever being written or re-read as such. */
+int bsp_matmul_umma_softmax(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
+                            int64_t n_out, float* stats, float scale,
+                            const int32_t* panel_first, int64_t n_panels, const int32_t* step_offsets,
+                            const int32_t* steps, const int32_t* touched, const int32_t* unit_panel,
+                            const int32_t* unit_step, int32_t n_units, int32_t* sched, int width,
+                            int bs, int dtype, int32_t* status_word, void* stream);
+
+/* Second half: with M = max over the blocks of a block row of m and
+ * L = sum over them of l * exp(m - M), out = e * exp(m - M) / L, converted to
+ * `out_dtype` (BSP_F16 / BSP_BF16 / BSP_F32).  row_first: int32
+ * (n_block_rows + 1), index of the first compressed block of every block row
+ * of the layout (a block row's blocks are consecutive in the compressed
+ * tensor).  Same result as softmax_forward, blksprs/ops/softmax.py:93-144, on
+ * the scaled scores, followed by a cast. */
+int bsp_softmax_normalize(const void* e, int in_dtype, const float* stats, int64_t n_blocks,
+                          const int32_t* row_first, int64_t n_block_rows, int bs, void* out,
+                          int out_dtype, void* stream);
+
 /* ---- the sparse linear helper (bias and chunked weight gradient) -------- */
 
 /* out[p, r, c] = x[p, r, c] + bias[lut[p][2] * bs + c] for the n_blocks rows

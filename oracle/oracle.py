@@ -187,6 +187,23 @@ def softmax_backward(grad_out: Tensor, out: Tensor, layout, bs: int) -> Tensor:
     return to_sparse(od * (gd - s), layout, bs).to(out.dtype)
 
 
+def matmul_softmax(x: Tensor, lx, y: Tensor, ly, lo, bs: int, scale: float) -> Tensor:
+    """The attention-by-parts chain of the reference's benchmark (test/cases/test_blocksparse.py:1517-1529):
+    ``softmax(matmul(x, y) * scale)`` over the active blocks of each output row, in float64.  Active output
+    blocks without a common inner block hold zeros (blksprs/ops/matmul.py:187, 245-253) and take part."""
+    scores = to_sparse(torch.matmul(to_dense(x.double(), lx, bs), to_dense(y.double(), ly, bs)), lo, bs) * scale
+    return softmax(scores, lo, bs)
+
+
+def matmul_softmax_backward(grad_out: Tensor, x: Tensor, lx, y: Tensor, ly, lo, bs: int, scale: float):
+    """Gradients of :func:`matmul_softmax` with respect to ``x`` and ``y`` (float64): softmax backward
+    (blksprs/ops/softmax.py:157-208), the scale, then the two products of the matmul backward
+    (blksprs/ops/matmul.py:130-145)."""
+    probs = matmul_softmax(x, lx, y, ly, lo, bs, scale)
+    grad_scores = softmax_backward(grad_out.double(), probs, lo, bs) * scale
+    return matmul_backward(grad_scores, x.double(), lx, y.double(), ly, lo, bs, accumulate=torch.float64)
+
+
 # ---- linear layer on a compressed tensor ---------------------------------------------
 
 def linear(x: Tensor, layout, bs: int, weight: Tensor, bias: Tensor | None = None):
