@@ -1,7 +1,8 @@
 """Small timing probes of the kernels around the matmul (conversion, softmax) and of the public
 matmul op over every dtype and block size; run through ``bench.py``.
 
-``python bench.py --probe softmax|conversion [--small]`` prints one line per case with the achieved
+``python bench.py --probe attention [--small]`` times the attention-score chain (separate ops against the
+fused ``matmul_softmax``).  ``python bench.py --probe softmax|conversion [--small]`` prints one line per case with the achieved
 bandwidth (algorithmic bytes / CUDA-event time).  ``--small`` runs one case of a few hundred MB, the
 size used for profiler captures.  ``python bench.py --probe matmul`` times the public matmul op
 (forward, forward + backward) for every dtype and block size on a 16 x 2048^3 problem with 25 %
@@ -103,7 +104,17 @@ def matmul(small: bool, iters: int) -> None:
     bs.utils.enable_validation()
 
 
-PROBES = {"softmax": softmax, "conversion": conversion, "matmul": matmul}
+def attention(small: bool, iters: int) -> None:
+    """softmax(scale * Q K^T) on the banded causal layout of the attention-score workload, as separate ops
+    and as the fused op, then P V (``bench.attention_chain_record``); ``--small`` runs 32 of the 512 batches."""
+    import json
+
+    import bench
+    rec = bench.attention_chain_record(torch.device("cuda", 0), bench.measured_peaks(), batch=32 if small else None)
+    print(json.dumps(rec))
+
+
+PROBES = {"softmax": softmax, "conversion": conversion, "matmul": matmul, "attention": attention}
 
 
 def run(what: str, small: bool, iters: int) -> None:

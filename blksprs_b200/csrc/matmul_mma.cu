@@ -253,8 +253,11 @@ matmul_mma_kernel(const T* __restrict__ a, int64_t n_a, const T* __restrict__ b,
 // ---- warp-autonomous streaming kernel for block sizes 16 and 32 ----------------------------
 
 template <typename T, int BS> struct StreamCfg {
-    // ring depth per warp: the tiles are small, so depth is what hides the L2 / HBM latency
-    static constexpr int kStages = sizeof(T) == 2 ? (BS == 16 ? 8 : 4) : (BS == 16 ? 6 : 2);
+    // Ring depth per warp.  The loop is bound by instruction issue and by the latency of dependent
+    // mma.sync instructions on a block's few accumulators, not by memory latency (profiler: no
+    // long-scoreboard stalls at 3 warps per scheduler, issue slots 47 % used), so the ring is kept
+    // short to fit more warps per SM: 36 / 12 warps for 16-bit blocks of 16 / 32, 24 / 8 for fp32.
+    static constexpr int kStages = sizeof(T) == 2 ? (BS == 16 ? 4 : 3) : (BS == 16 ? 3 : 2);
     static constexpr int kWarps = 4;
 };
 
