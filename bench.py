@@ -650,11 +650,12 @@ def median(v):
     return s[len(s) // 2]
 
 
-def n_regions(est_ms_per_step: float, steps: int, want: int = 30, budget_s: float = 4.0) -> int:
-    """R >= ``want`` regions, more for very short ones (the clock sampler needs time), within a budget."""
+def n_regions(est_ms_per_step: float, steps: int, want: int = 30, budget_s: float = 6.0) -> int:
+    """R >= ``want`` regions and at least 1.5 s of timed work in all (a steady power and clock state, enough
+    clock samples), within a budget."""
     region_s = max(est_ms_per_step * steps * 1e-3, 1e-6)
-    r = max(want, int(0.5 / region_s))
-    return max(5, min(r, int(budget_s / region_s), 2000))
+    r = max(want, int(1.5 / region_s) + 1)
+    return max(5, min(r, int(budget_s / region_s), 4000))
 
 
 def sub_record(name, dev, args, peaks):
@@ -734,7 +735,13 @@ def attention_chain_record(dev, peaks, batch=None):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / n
 
-    p_chain, p_fused = chain(), fused()
+    p_chain, p_fused = chain(), fused()   # also builds the caches and plans
+    pv(p_fused)
+    torch.cuda.profiler.start()   # one warm pass of each form, for a profiler attached with "--profile-from-start off"
+    chain()
+    fused()
+    pv(p_fused)
+    torch.cuda.profiler.stop()
     diff = float((p_chain.float() - p_fused.float()).abs().max()) / max(float(p_chain.float().abs().max()), 1e-30)
     t_chain, t_fused = timed(chain), timed(fused)
     t_pv = timed(lambda: pv(p_fused))
@@ -799,7 +806,9 @@ def run_gpu_arm(args):
     R = args.regions or n_regions(probe, args.steps)
     with ClockSampler(physical_gpu_index(local)) as clocks:
         barrier()
+        torch.cuda.profiler.start()   # a profiler attached with "--profile-from-start off" sees the timed region only
         region_ms = time_regions(graph, prob.step, args.steps, n_sets, R)
+        torch.cuda.profiler.stop()
         barrier()
     check_device_status(dev)
     region_t = torch.tensor(region_ms, dtype=torch.float64, device=dev)

@@ -314,7 +314,8 @@ matmul_mma_stream_kernel(const T* __restrict__ a, int64_t n_a, const T* __restri
         const int my_off = offsets[p0 + min(lane, nb)];
         const int q_begin = __shfl_sync(0xffffffffu, my_off, 0);
         const int q_end = offsets[p0 + nb];
-        const int n_pairs = q_end - q_begin;
+        // without operand blocks there is nothing to multiply: every block of the chunk is written as zeros
+        const int n_pairs = (n_a > 0 && n_b > 0) ? q_end - q_begin : 0;
 
         // pair records, 32 at a time: this window and the next one
         auto load_window = [&](int w) -> int2 {
@@ -333,32 +334,30 @@ matmul_mma_stream_kernel(const T* __restrict__ a, int64_t n_a, const T* __restri
                 win_next = load_window(win_no + 1);
             }
             const int xa = __shfl_sync(0xffffffffu, win.x, s & 31);
-            const int xb = __shfl_sync(0xffffffffu, win.y, s & 31);
-            ia = xa < 0 ? -1 : (xa & 0x3fffffff);  // bit 30 marks a block's last pair (not used here)
-            ib = xb;
+            ib = __shfl_sync(0xffffffffu, win.y, s & 31);
+            ia = xa & 0x3fffffff;  // bit 30 marks a block's last pair (not used here); a negative value stays out of range
         };
-        // copies the two operand blocks of stream position s into its ring stage; the validity of
-        // the indices is returned (nothing is copied for a bad pair)
-        auto issue = [&](int s) -> bool {
+        // copies the two operand blocks of stream position s into its ring stage.  Indices outside the
+        // operands are reported in the status word and replaced by block 0 (which exists whenever a
+        // pair does), so that the access stays inside the operands and the loop needs no special case.
+        auto issue = [&](int s) {
             int ia, ib;
             record(s, ia, ib);
-            const bool ok = ia >= 0 && ia < n_a && ib >= 0 && ib < n_b;
-            if (ok) {
-                const T* ga = a + ia * BLK;
-                const T* gb = b + ib * BLK;
-                T* sa = ring + (s % S) * STAGE_ELEMS;
-                T* sb = sa + BS * ALD;
+            if ((unsigned)ia >= (unsigned long long)n_a || (unsigned)ib >= (unsigned long long)n_b) {
+                if (status_word && lane == 0) *status_word = BSP_ERR_DEVICE_RANGE;
+                ia = ib = 0;
+            }
+            const T* ga = a + ia * BLK;
+            const T* gb = b + ib * BLK;
+            T* sa = ring + (s % S) * STAGE_ELEMS;
+            T* sb = sa + BS * ALD;
 #pragma unroll
-                for (int i = lane; i < BS * CPR; i += 32) {
-                    const int r = i / CPR, cc = (i % CPR) * CHUNK;
-                    cp_async16(sa + r * ALD + cc, ga + r * BS + cc);
-                    cp_async16(sb + r * BLD + cc, gb + r * BS + cc);
-                }
-            } else if (status_word && lane == 0) {
-                *status_word = BSP_ERR_DEVICE_RANGE;
+            for (int i = lane; i < BS * CPR; i += 32) {
+                const int r = i / CPR, cc = (i % CPR) * CHUNK;
+                cp_async16(sa + r * ALD + cc, ga + r * BS + cc);
+                cp_async16(sb + r * BLD + cc, gb + r * BS + cc);
             }
             cp_async_commit();
-            return ok;
         };
 
         clear_acc();
@@ -371,9 +370,8 @@ matmul_mma_stream_kernel(const T* __restrict__ a, int64_t n_a, const T* __restri
         };
         int blk_end = block_end(0);
 
-        uint32_t ok_mask = 0;  // bit (s % 32): pair s had valid indices
         const int lead = min(S - 1, n_pairs);
-        for (int s = 0; s < lead; ++s) ok_mask |= (issue(s) ? 1u : 0u) << (s & 31);
+        for (int s = 0; s < lead; ++s) issue(s);
         for (int s = 0; s < n_pairs; ++s) {
             // blocks that end before this pair (the previous pair's block, and empty ones) are written
             while (s == blk_end && blk < nb) {
@@ -384,14 +382,13 @@ matmul_mma_stream_kernel(const T* __restrict__ a, int64_t n_a, const T* __restri
             }
             const int sn = s + S - 1;
             if (sn < n_pairs) {
-                const bool okn = issue(sn);
-                ok_mask = (ok_mask & ~(1u << (sn & 31))) | ((okn ? 1u : 0u) << (sn & 31));
+                issue(sn);
                 cp_async_wait<S - 1>();
             } else {
                 cp_async_wait<0>();
             }
             __syncwarp();
-            if ((ok_mask >> (s & 31)) & 1u) {
+            {
                 const T* sa = ring + (s % S) * STAGE_ELEMS;
                 const T* sb = sa + BS * ALD;
 #pragma unroll

@@ -177,6 +177,11 @@ def _matmul_eager(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_ou
             # validate_sparsity has just confirmed the block counts against the layouts
             plans.n_x, plans.n_y = x.size(0), y.size(0)
             plans.layouts_validated = True
+        if torch.is_grad_enabled() and (x.requires_grad or y.requires_grad):
+            # a training step will need them: build the plans of dX and dY with the forward plan, so that all
+            # cold-path device reads of a layout triple happen in its first forward call
+            _backward_plans(plans, layout_cache["packed_indices_x"], layout_cache["packed_indices_y"], x.size(0),
+                            y.size(0))
 
     out = _BlockSparseMatmul.apply(x, y, layout_cache["packed_indices_x"], layout_cache["packed_indices_y"],
                                    plans, sparsity_block_size)

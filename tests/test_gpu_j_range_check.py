@@ -3,9 +3,9 @@
 Both matmul kernels compare every operand block index they take from a plan with the operand's block
 count before they use it (the reference guards its loads with masks, blksprs/ops/matmul.py:204-209,
 230-231; invalid metadata must never become an out-of-range access).  A bad index makes the kernel
-write ``BSP_ERR_DEVICE_RANGE`` into the status word; the mma.sync kernel skips the pair, the tcgen05
-kernel substitutes block 0.  Here one index of an otherwise valid plan is replaced by ``n`` (one past
-the end) or by ``-2``; the operand buffers are allocated with a few blocks of slack, so that even a
+write ``BSP_ERR_DEVICE_RANGE`` into the status word and use block 0 in place of the bad index (the
+mma.sync tile kernel for larger blocks skips the pair).  Here one index of an otherwise valid plan is
+replaced by ``n`` (one past the end) or by ``-2``; the operand buffers are allocated with a few blocks of slack, so that even a
 wrong guard could not leave the allocation.  Expected: the status word holds the range code, every
 output block that does not depend on the corrupted entry equals the clean run bit for bit, and the
 device keeps working.
@@ -68,7 +68,7 @@ def _run_umma(product, sp, steps, x, y, n_x, n_y, bs):
 
 @pytest.mark.parametrize("bad", ["past_end", "minus_two"])
 @pytest.mark.parametrize("operand", ["a", "b"])
-def test_mma_kernel_flags_and_skips_bad_pair(bad, operand):
+def test_mma_kernel_flags_bad_pair(bad, operand):
     from blksprs_b200 import _cabi
     bs = 32
     product, x, y, n_x, n_y = _setup(bs, torch.float16)
