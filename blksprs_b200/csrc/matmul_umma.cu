@@ -52,8 +52,6 @@ namespace {
 constexpr uint32_t kCtrlLast = 0x100u;
 // Slots of the per-CTA queue of unit numbers (dynamic scheduling).
 constexpr int kUnitQueue = 8;
-// Producers ask L2 for the operand pieces of their next ring entry one ring turn ahead.
-constexpr bool kPrefetchL2 = true;
 
 // Per (block size, panel width): ring depth, accumulator groups (of G x bs tensor-memory
 // columns each) and resident CTAs per SM.  Shared memory: stages x (1 + G) x bs x 128 bytes.
@@ -362,16 +360,15 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     for (int e = first_entry(ub, goff); e < ue && alive; e += S) {
                         if (!have) load_rec(e, c0, c1);
                         // fetch this lane's next record now: later in this unit, or its first in the next
-                        int ne = e + S;
+                        const int ne = e + S;
                         bool nhave = false;
                         if (ne < ue) {
                             load_rec(ne, n0, n1);
                             nhave = true;
                         } else {
                             peek_next();
-                            ne = first_entry(nub, ngoff);
-                            if (nu >= 0 && ne < nue) {
-                                load_rec(ne, n0, n1);
+                            if (nu >= 0 && first_entry(nub, ngoff) < nue) {
+                                load_rec(first_entry(nub, ngoff), n0, n1);
                                 nhave = true;
                             }
                         }
@@ -431,35 +428,6 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                     if (status_word) *status_word = BSP_ERR_DEVICE_TIMEOUT;
                                     alive = false;
                                     break;
-                                }
-                            }
-                        }
-                        // The lane's next entry is copied one turn of the ring from now.  Asking L2 for its
-                        // operand pieces already (a hint, no shared memory or barrier involved) turns that
-                        // copy from a DRAM access into an L2 hit, which is what lets a ring of S entries
-                        // cover the copy latency.
-                        if (kPrefetchL2 && nhave && alive) {
-                            const int nkc = ne % KC;
-                            const int pa = n0.x;
-                            const int pb[4] = {n0.y, n0.z, n0.w, n1.x};
-                            const uint32_t npresent = (uint32_t)n1.y & 0xFu;
-                            if (pa >= 0 && pa < n_a) {
-                                if (A_MN) {
-#pragma unroll
-                                    for (int h = 0; h < H; ++h) tma_prefetch_2d(&map_a, h * KE, pa * BS + nkc * KE);
-                                } else {
-                                    tma_prefetch_2d(&map_a, nkc * KE, pa * BS);
-                                }
-                            }
-#pragma unroll
-                            for (int q = 0; q < G; ++q) {
-                                if (((npresent >> q) & 1u) && pb[q] >= 0 && pb[q] < n_b) {
-                                    if (B_MN) {
-#pragma unroll
-                                        for (int h = 0; h < H; ++h) tma_prefetch_2d(&map_b, h * KE, pb[q] * BS + nkc * KE);
-                                    } else {
-                                        tma_prefetch_2d(&map_b, nkc * KE, pb[q] * BS);
-                                    }
                                 }
                             }
                         }

@@ -258,7 +258,10 @@ int bsp_panel_fill(const int64_t* lut_out, const int32_t* panel_first, int64_t n
  *               Otherwise device int32[2], zero before the first launch: after
  *               its first unit a CTA draws its next units from this counter, so
  *               slower CTAs take fewer; the kernel leaves both words zero again.
- *               One launch at a time per `sched` buffer.
+ *               One launch at a time per `sched` buffer: a launch recorded
+ *               into a CUDA graph needs a buffer of its own (a replay can
+ *               overlap later launches of the capture stream), and such a
+ *               graph must not be replayed concurrently with itself.
  *   bias        NULL, or one element of the data dtype per output column
  *               (16-byte aligned): out[p, r, c] additionally gets
  *               bias[out_lut[p][2] * bs + c], added to the fp32 accumulator
