@@ -627,6 +627,20 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         alive = __all_sync(0xffffffffu, alive);
                         if (!alive) break;
                         tc_fence_after();
+                        // The accumulator group goes back to the MMA warp as soon as this warp's last read of
+                        // it has landed in registers; conversion, exchange and stores follow after that.
+                        bool released = false;
+                        auto release_group = [&]() {
+                            if (!released) {
+                                tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(tempty_bar + 8 * grp);
+                                released = true;
+                            }
+                        };
+                        const int touched_here = tmask & ((1 << g) - 1);
+                        const int last_q = touched_here ? 31 - __clz(touched_here) : -1;  // last block that holds sums
+                        const uint32_t tgroup = tmem_base + grp * (G * BS) + ((uint32_t)(wq * 32) << 16);
                         for (int q = 0; q < g; ++q) {
                             T* o = out + (int64_t)(first + q) * BS * BS;
                             const T* brow = bias_of(first + q);
@@ -634,12 +648,13 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 zero_quarter(o, brow, first + q);
                                 continue;
                             }
-                            const uint32_t taddr = tmem_base + grp * (G * BS) + q * BS + ((uint32_t)(wq * 32) << 16);
+                            const uint32_t taddr = tgroup + q * BS;
                             if constexpr (BS == 64) {
                                 // M = 64: the warp's 16 rows x 64 columns in one load; all 32 lanes get data
                                 uint32_t v[32];
                                 tc_ld16x64(taddr, v);
                                 tc_wait_ld();
+                                if (q == last_q) release_group();
                                 const int qd = lane & 3;
                                 const int r0 = wq * 16 + (lane >> 2);  // and r0 + 8
                                 if (BIAS && brow) {
@@ -736,6 +751,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                     tc_ld32(taddr + half * 64, v);
                                     tc_ld32(taddr + half * 64 + 32, v + 32);
                                     tc_wait_ld();
+                                    if (q == last_q && half == 1) release_group();
                                     if constexpr (SOFTMAX) {
 #pragma unroll
                                         for (int e = 0; e < 64; ++e) {
@@ -773,6 +789,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 uint32_t v[32];
                                 tc_ld32(taddr + c0, v);
                                 tc_wait_ld();
+                                if (q == last_q && c0 == BS - 32) release_group();
                                 if (BIAS && brow) {
                                     // every lane adds the same 32 bias values (broadcast loads)
                                     constexpr int EPV = 16 / (int)sizeof(T);  // elements per 16-byte load
@@ -813,9 +830,7 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             }
                             }
                         }
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(tempty_bar + 8 * grp);
+                        release_group();  // a panel whose steps touched none of its blocks
                         if (++grp == NG) { grp = 0; grp_phase ^= 1u; }
                     }
                 }
