@@ -114,7 +114,35 @@ def attention(small: bool, iters: int) -> None:
     print(json.dumps(rec))
 
 
-PROBES = {"softmax": softmax, "conversion": conversion, "matmul": matmul, "attention": attention}
+def nocache(small: bool, iters: int) -> None:
+    """Calls WITHOUT a ``layout_cache`` (the reference's default): time per forward call on unchanged layout
+    objects, with the library-owned caches on and off, and the reference's op called the same way."""
+    import os
+    import sys
+
+    import bench
+    ref = None
+    try:
+        ref = bench._import_reference()
+    except Exception as exc:
+        print(f"reference not importable: {exc!r}")
+    for name in ("config1", "config2") + (() if small else ("config5",)):
+        lx, ly, lo, bsz, dtype = bench.workload_layouts(name, batch=8 if name == "config5" else None)
+        x, y, _ = bench.workload_values(name, lx, ly, lo, bsz, dtype, seed=0, device="cuda")
+        lxd, lyd, lod = lx.cuda(), ly.cuda(), lo.cuda()
+        bs.utils.set_implicit_layout_caches(True)
+        warm = _time(lambda: bs.ops.matmul(x, lxd, y, lyd, lod, bsz), iters)
+        bs.utils.set_implicit_layout_caches(False)
+        cold = _time(lambda: bs.ops.matmul(x, lxd, y, lyd, lod, bsz), iters)
+        bs.utils.set_implicit_layout_caches(True)
+        line = f"{name}: forward call without layout_cache: {warm * 1e3:.0f} us (library-owned cache), {cold * 1e3:.0f} us (rebuild every call)"
+        if ref is not None:
+            t = _time(lambda: ref.ops.matmul(x, lxd, y, lyd, lod, bsz), iters)
+            line += f", reference {t * 1e3:.0f} us"
+        print(line)
+
+
+PROBES = {"nocache": nocache, "softmax": softmax, "conversion": conversion, "matmul": matmul, "attention": attention}
 
 
 def run(what: str, small: bool, iters: int) -> None:

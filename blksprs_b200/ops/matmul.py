@@ -17,7 +17,7 @@ from .. import _cabi
 from ..plan import Product
 from ..utils.blksprs_tensor import BlksprsTensor
 from ..utils.tools import build_layout_indices, build_packed_indices, cast_for_autocast, count_active_blocks, \
-    finalize_layout_cache, layout_cache_is_current, prepare_layout_cache
+    finalize_layout_cache, implicit_layout_cache, layout_cache_is_current, prepare_layout_cache
 from ..utils.validation import ensure_contiguous, validate_contiguous, validate_device, validate_dimensions, \
     validate_dtype_float, validate_shape, validate_sparsity, validate_sparsity_block_size, \
     validate_sparsity_layout, validation_enabled
@@ -159,6 +159,9 @@ def _matmul_eager(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_ou
 
     # A warm cache (same layout objects, unchanged) has the plans and already knows that the layouts are
     # valid and how many blocks each holds: only the checks on x and y remain, without a device read.
+    if layout_cache is None:
+        # no caller-owned cache: a small library-owned one, with the same reuse rule (tools.implicit_layout_cache)
+        layout_cache = implicit_layout_cache("matmul", sparsity_layout_x, sparsity_layout_y, sparsity_layout_output)
     plans = None
     if layout_cache_is_current(layout_cache, "matmul", sparsity_layout_x, sparsity_layout_y,
                                sparsity_layout_output):

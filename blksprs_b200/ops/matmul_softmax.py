@@ -23,7 +23,7 @@ from torch import Tensor
 from .. import _cabi
 from ..plan import status_word
 from ..utils.blksprs_tensor import BlksprsTensor
-from ..utils.tools import cast_for_autocast, layout_cache_is_current
+from ..utils.tools import cast_for_autocast, implicit_layout_cache, layout_cache_is_current
 from ..utils.validation import ensure_contiguous, validation_enabled
 from .matmul import _PLANS, _MatmulPlans, _backward_plans, _validate_cold, _validate_warm, \
     matmul_build_layout_cache
@@ -134,6 +134,9 @@ def _matmul_softmax_eager(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_l
         out_dtype = x.dtype
     if out_dtype not in _OUT_DTYPES:
         raise ValueError("Output dtype must be float16, bfloat16, or float32")
+    if layout_cache is None:
+        # no caller-owned cache: a small library-owned one, with the same reuse rule (tools.implicit_layout_cache)
+        layout_cache = implicit_layout_cache("matmul", sparsity_layout_x, sparsity_layout_y, sparsity_layout_output)
     plans = None
     if layout_cache_is_current(layout_cache, "matmul", sparsity_layout_x, sparsity_layout_y, sparsity_layout_output):
         plans = layout_cache.get(_PLANS)

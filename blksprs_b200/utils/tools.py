@@ -8,6 +8,8 @@ The cache protocol follows blksprs/utils/tools.py:60-156.
 """
 from __future__ import annotations
 
+import threading
+from collections import OrderedDict
 from typing import Any
 
 import torch
@@ -156,6 +158,55 @@ def layout_cache_is_current(layout_cache: LayoutCache | None, operation: str, *v
             and _cache_contents_state(layout_cache) == recorded)
 
 
+# Calls that pass no ``layout_cache`` (the reference's default, under which it rebuilds all metadata on
+# every call) get one from a small library-owned LRU keyed like a caller-owned cache: operation name plus
+# identity / version / shape / stride / dtype / device / requires_grad of every layout.  An entry holds
+# references to its layouts (so their ids cannot be recycled while it lives) and is subject to the same
+# reuse rule as any cache: an in-place change of a layout bumps its version and misses.  Results are the
+# same as without it; only the rebuild (LUT kernels, plan kernels and their device reads) is saved.
+IMPLICIT_CACHE_ENTRIES = 4
+_implicit_caches: "OrderedDict[tuple, LayoutCache]" = OrderedDict()
+_implicit_lock = threading.Lock()
+_implicit_enabled = True
+
+
+def implicit_layout_cache(operation: str, *values: object) -> LayoutCache | None:
+    """The library-owned cache for a call without ``layout_cache``; None when disabled or when a layout
+    is an inference tensor (no version counter: never reusable)."""
+    if not _implicit_enabled:
+        return None
+    for value in values:
+        if isinstance(value, Tensor) and torch.is_inference(value):
+            return None
+    key = _cache_key(operation, values)
+    with _implicit_lock:
+        cache = _implicit_caches.get(key)
+        if cache is None:
+            cache = {}
+            _implicit_caches[key] = cache
+            while len(_implicit_caches) > IMPLICIT_CACHE_ENTRIES:
+                _implicit_caches.popitem(last=False)
+        else:
+            _implicit_caches.move_to_end(key)
+    return cache
+
+
+def clear_implicit_layout_caches() -> None:
+    """Drops the library-owned caches of calls made without ``layout_cache`` (and the layouts, LUTs and
+    plans they hold)."""
+    with _implicit_lock:
+        _implicit_caches.clear()
+
+
+def set_implicit_layout_caches(enabled: bool) -> None:
+    """Switches the library-owned caches on or off (off: every call without ``layout_cache`` rebuilds its
+    metadata, as the reference does)."""
+    global _implicit_enabled
+    _implicit_enabled = bool(enabled)
+    if not enabled:
+        clear_implicit_layout_caches()
+
+
 def prepare_layout_cache(layout_cache: LayoutCache | None, operation: str, *values: object) -> LayoutCache:
     """Returns a cache dict for ``operation`` that is empty unless it was built for exactly these inputs.
 
@@ -164,6 +215,8 @@ def prepare_layout_cache(layout_cache: LayoutCache | None, operation: str, *valu
     and every scalar argument are unchanged, and nothing stored in the cache
     was replaced or mutated since ``finalize_layout_cache``.
     """
+    if layout_cache is None:
+        layout_cache = implicit_layout_cache(operation, *values)
     if layout_cache is None:
         layout_cache = {}
     held: list[Tensor] = []

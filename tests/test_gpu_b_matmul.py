@@ -304,3 +304,35 @@ def test_bounded_wait_expires_with_a_status_instead_of_hanging():
     assert lib.bsp_selftest_wait_limit(0, word.data_ptr(), None) == _cabi.ERR_INVALID_ARG
     # the device still works
     assert float((torch.ones(4, device=DEV) * 2).sum()) == 8.0
+
+
+def test_calls_without_a_cache_reuse_library_owned_metadata():
+    """``layout_cache=None`` (the reference's default) does not rebuild LUTs and plans on every call: a small
+    library-owned cache with the caller-cache reuse rule serves repeated calls on the same layout objects."""
+    import blksprs_b200 as bs
+    from blksprs_b200.ops.matmul import _PLANS
+    from blksprs_b200.utils import tools
+    case = make_case(2, 256, 192, 128, 64, 0.5, torch.bfloat16, seed=31, out_layout="exact")
+    lx, ly, lo = (case[k].to(DEV) for k in ("lx", "ly", "lo"))
+    x, y = case["x"].to(DEV), case["y"].to(DEV)
+    tools.clear_implicit_layout_caches()
+    first = bs.ops.matmul(x, lx, y, ly, lo, 64)
+    entry = tools.implicit_layout_cache("matmul", lx, ly, lo)
+    plans = entry[_PLANS]
+    second = bs.ops.matmul(x, lx, y, ly, lo, 64)
+    assert torch.equal(first, second)
+    assert tools.implicit_layout_cache("matmul", lx, ly, lo)[_PLANS] is plans          # reused, not rebuilt
+    # wrong block count on a warm entry: the reference's message, without a device read
+    with pytest.raises(ValueError, match="Mismatch between sparsity layout and blocks"):
+        bs.ops.matmul(x[:-1], lx, y, ly, lo, 64)
+    lo.logical_or_(lo)                                                                 # same content, new version
+    third = bs.ops.matmul(x, lx, y, ly, lo, 64)
+    assert torch.equal(first, third)
+    assert tools.implicit_layout_cache("matmul", lx, ly, lo)[_PLANS] is not plans      # rebuilt for the new version
+    bs.utils.set_implicit_layout_caches(False)
+    try:
+        fourth = bs.ops.matmul(x, lx, y, ly, lo, 64)
+        assert torch.equal(first, fourth)
+        assert tools.implicit_layout_cache("matmul", lx, ly, lo) is None
+    finally:
+        bs.utils.set_implicit_layout_caches(True)
