@@ -327,35 +327,42 @@ matmul_mma_stream_kernel(const T* __restrict__ a, int64_t n_a, const T* __restri
         // flight for 32 issues before its first record is needed)
         int2 win = load_window(0), win_next = load_window(1);
         int win_no = 0;
-        auto record = [&](int s, int& ia, int& ib) {
+        // the record of the next position to be issued is fetched (two shuffles) right after the previous
+        // issue, so that its latency is hidden behind the multiplications in between
+        int nia = 0, nib = 0;
+        auto fetch_record = [&](int s) {
             if ((s >> 5) > win_no) {
                 win = win_next;
                 ++win_no;
                 win_next = load_window(win_no + 1);
             }
             const int xa = __shfl_sync(0xffffffffu, win.x, s & 31);
-            ib = __shfl_sync(0xffffffffu, win.y, s & 31);
-            ia = xa & 0x3fffffff;  // bit 30 marks a block's last pair (not used here); a negative value stays out of range
+            nib = __shfl_sync(0xffffffffu, win.y, s & 31);
+            nia = xa & 0x3fffffff;  // bit 30 marks a block's last pair (not used here); a negative value stays out of range
         };
-        // copies the two operand blocks of stream position s into its ring stage.  Indices outside the
-        // operands are reported in the status word and replaced by block 0 (which exists whenever a
-        // pair does), so that the access stays inside the operands and the loop needs no special case.
+        // copies the two operand blocks of stream position s into its ring stage and commits the group;
+        // beyond the end of the stream only an empty group is committed, which keeps the group count
+        // per iteration constant.  Indices outside the operands are reported in the status word and
+        // replaced by block 0 (which exists whenever a pair does), so that the access stays inside the
+        // operands and the loop needs no special case.
         auto issue = [&](int s) {
-            int ia, ib;
-            record(s, ia, ib);
-            if ((unsigned)ia >= (unsigned long long)n_a || (unsigned)ib >= (unsigned long long)n_b) {
-                if (status_word && lane == 0) *status_word = BSP_ERR_DEVICE_RANGE;
-                ia = ib = 0;
-            }
-            const T* ga = a + ia * BLK;
-            const T* gb = b + ib * BLK;
-            T* sa = ring + (s % S) * STAGE_ELEMS;
-            T* sb = sa + BS * ALD;
+            if (s < n_pairs) {
+                int ia = nia, ib = nib;
+                if ((unsigned)ia >= (unsigned long long)n_a || (unsigned)ib >= (unsigned long long)n_b) {
+                    if (status_word && lane == 0) *status_word = BSP_ERR_DEVICE_RANGE;
+                    ia = ib = 0;
+                }
+                const T* ga = a + ia * BLK;
+                const T* gb = b + ib * BLK;
+                T* sa = ring + (s % S) * STAGE_ELEMS;
+                T* sb = sa + BS * ALD;
 #pragma unroll
-            for (int i = lane; i < BS * CPR; i += 32) {
-                const int r = i / CPR, cc = (i % CPR) * CHUNK;
-                cp_async16(sa + r * ALD + cc, ga + r * BS + cc);
-                cp_async16(sb + r * BLD + cc, gb + r * BS + cc);
+                for (int i = lane; i < BS * CPR; i += 32) {
+                    const int r = i / CPR, cc = (i % CPR) * CHUNK;
+                    cp_async16(sa + r * ALD + cc, ga + r * BS + cc);
+                    cp_async16(sb + r * BLD + cc, gb + r * BS + cc);
+                }
+                if (s + 1 < n_pairs) fetch_record(s + 1);
             }
             cp_async_commit();
         };
@@ -370,9 +377,76 @@ matmul_mma_stream_kernel(const T* __restrict__ a, int64_t n_a, const T* __restri
         };
         int blk_end = block_end(0);
 
-        const int lead = min(S - 1, n_pairs);
-        for (int s = 0; s < lead; ++s) issue(s);
+        // fragments of one k-step of the pair in ring stage `st`
+        auto load_frags = [&](int st, int k0, uint32_t (&af)[MI][4], uint32_t (&bf)[NI][2]) {
+            const T* sa = ring + st * STAGE_ELEMS;
+            const T* sb = sa + BS * ALD;
+            if constexpr (Elem<T>::k16) {
+                const int q = lane >> 3, rr = lane & 7;
+#pragma unroll
+                for (int i = 0; i < MI; ++i) {
+                    const int m0 = i * 16;
+                    if constexpr (!A_TRANS) {
+                        ldmatrix_x4(af[i], sa + (m0 + rr + (q & 1) * 8) * ALD + k0 + (q >> 1) * 8);
+                    } else {
+                        ldmatrix_x4_trans(af[i], sa + (k0 + rr + (q >> 1) * 8) * ALD + m0 + (q & 1) * 8);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < NI; j += 2) {
+                    const int n0 = j * 8;
+                    uint32_t r4[4];
+                    if constexpr (B_NK) {
+                        ldmatrix_x4(r4, sb + (n0 + rr + (q >> 1) * 8) * BLD + k0 + (q & 1) * 8);
+                    } else {
+                        ldmatrix_x4_trans(r4, sb + (k0 + rr + (q & 1) * 8) * BLD + n0 + (q >> 1) * 8);
+                    }
+                    bf[j][0] = r4[0]; bf[j][1] = r4[1];
+                    bf[j + 1][0] = r4[2]; bf[j + 1][1] = r4[3];
+                }
+            } else {
+                auto A_at = [&](int m, int k) -> float {
+                    return A_TRANS ? (float)sa[k * ALD + m] : (float)sa[m * ALD + k];
+                };
+                auto B_at = [&](int k, int n) -> float {
+                    return B_NK ? (float)sb[n * BLD + k] : (float)sb[k * BLD + n];
+                };
+#pragma unroll
+                for (int i = 0; i < MI; ++i) {
+                    const int m0 = i * 16;
+                    af[i][0] = f32_to_tf32(A_at(m0 + g, k0 + t4));
+                    af[i][1] = f32_to_tf32(A_at(m0 + g + 8, k0 + t4));
+                    af[i][2] = f32_to_tf32(A_at(m0 + g, k0 + t4 + 4));
+                    af[i][3] = f32_to_tf32(A_at(m0 + g + 8, k0 + t4 + 4));
+                }
+#pragma unroll
+                for (int j = 0; j < NI; ++j) {
+                    const int n0 = j * 8;
+                    bf[j][0] = f32_to_tf32(B_at(k0 + t4, n0 + g));
+                    bf[j][1] = f32_to_tf32(B_at(k0 + t4 + 4, n0 + g));
+                }
+            }
+        };
+        auto multiply = [&](const uint32_t (&af)[MI][4], const uint32_t (&bf)[NI][2]) {
+#pragma unroll
+            for (int i = 0; i < MI; ++i)
+#pragma unroll
+                for (int j = 0; j < NI; ++j) Elem<T>::mma(acc[i][j], af[i], bf[j]);
+        };
+
+        // S - 1 groups are committed ahead; every iteration commits one more, so that "at most S - 2
+        // groups pending" always means: the group of position s has landed
+        if (n_pairs > 0) fetch_record(0);
+        for (int s = 0; s < S - 1; ++s) issue(s);
         for (int s = 0; s < n_pairs; ++s) {
+            cp_async_wait<S - 2>();
+            __syncwarp();
+            // the first k-step's fragments are requested, then the copies of position s + S - 1 are issued
+            // (into the stage that position s - 1 has finished with) while those loads are in flight
+            uint32_t af[MI][4];
+            uint32_t bf[NI][2];
+            load_frags(s % S, 0, af, bf);
+            issue(s + S - 1);
             // blocks that end before this pair (the previous pair's block, and empty ones) are written
             while (s == blk_end && blk < nb) {
                 write_block(p0 + blk);
@@ -380,74 +454,15 @@ matmul_mma_stream_kernel(const T* __restrict__ a, int64_t n_a, const T* __restri
                 ++blk;
                 blk_end = block_end(blk);
             }
-            const int sn = s + S - 1;
-            if (sn < n_pairs) {
-                issue(sn);
-                cp_async_wait<S - 1>();
-            } else {
-                cp_async_wait<0>();
+            multiply(af, bf);
+#pragma unroll
+            for (int k0 = KSTEP; k0 < BS; k0 += KSTEP) {
+                load_frags(s % S, k0, af, bf);
+                multiply(af, bf);
             }
-            __syncwarp();
-            {
-                const T* sa = ring + (s % S) * STAGE_ELEMS;
-                const T* sb = sa + BS * ALD;
-#pragma unroll
-                for (int k0 = 0; k0 < BS; k0 += KSTEP) {
-                    uint32_t af[MI][4];
-                    uint32_t bf[NI][2];
-                    if constexpr (Elem<T>::k16) {
-                        const int q = lane >> 3, rr = lane & 7;
-#pragma unroll
-                        for (int i = 0; i < MI; ++i) {
-                            const int m0 = i * 16;
-                            if constexpr (!A_TRANS) {
-                                ldmatrix_x4(af[i], sa + (m0 + rr + (q & 1) * 8) * ALD + k0 + (q >> 1) * 8);
-                            } else {
-                                ldmatrix_x4_trans(af[i], sa + (k0 + rr + (q >> 1) * 8) * ALD + m0 + (q & 1) * 8);
-                            }
-                        }
-#pragma unroll
-                        for (int j = 0; j < NI; j += 2) {
-                            const int n0 = j * 8;
-                            uint32_t r4[4];
-                            if constexpr (B_NK) {
-                                ldmatrix_x4(r4, sb + (n0 + rr + (q >> 1) * 8) * BLD + k0 + (q & 1) * 8);
-                            } else {
-                                ldmatrix_x4_trans(r4, sb + (k0 + rr + (q & 1) * 8) * BLD + n0 + (q >> 1) * 8);
-                            }
-                            bf[j][0] = r4[0]; bf[j][1] = r4[1];
-                            bf[j + 1][0] = r4[2]; bf[j + 1][1] = r4[3];
-                        }
-                    } else {
-                        auto A_at = [&](int m, int k) -> float {
-                            return A_TRANS ? (float)sa[k * ALD + m] : (float)sa[m * ALD + k];
-                        };
-                        auto B_at = [&](int k, int n) -> float {
-                            return B_NK ? (float)sb[n * BLD + k] : (float)sb[k * BLD + n];
-                        };
-#pragma unroll
-                        for (int i = 0; i < MI; ++i) {
-                            const int m0 = i * 16;
-                            af[i][0] = f32_to_tf32(A_at(m0 + g, k0 + t4));
-                            af[i][1] = f32_to_tf32(A_at(m0 + g + 8, k0 + t4));
-                            af[i][2] = f32_to_tf32(A_at(m0 + g, k0 + t4 + 4));
-                            af[i][3] = f32_to_tf32(A_at(m0 + g + 8, k0 + t4 + 4));
-                        }
-#pragma unroll
-                        for (int j = 0; j < NI; ++j) {
-                            const int n0 = j * 8;
-                            bf[j][0] = f32_to_tf32(B_at(k0 + t4, n0 + g));
-                            bf[j][1] = f32_to_tf32(B_at(k0 + t4 + 4, n0 + g));
-                        }
-                    }
-#pragma unroll
-                    for (int i = 0; i < MI; ++i)
-#pragma unroll
-                        for (int j = 0; j < NI; ++j) Elem<T>::mma(acc[i][j], af[i], bf[j]);
-                }
-            }
-            __syncwarp();  // the stage may be refilled by the next iteration's copies
+            __syncwarp();  // all lanes are done with the stage before the next iteration refills it
         }
+        cp_async_wait<0>();
         // the chunk's remaining blocks: the last one with pairs, and empty ones behind it
         while (blk < nb) {
             write_block(p0 + blk);
