@@ -768,7 +768,9 @@ def run_gpu_arm(args):
     dev = torch.device("cuda", local)
     numa = bind_to_gpu_numa_node(physical_gpu_index(local))
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # a short collective timeout: a rank that fails must end the job quickly, never leave the others waiting
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     name = args.config
     peaks = measured_peaks()
 
@@ -804,6 +806,11 @@ def run_gpu_arm(args):
     torch.cuda.synchronize()
     probe = time_regions(graph, prob.step, args.steps, n_sets, 1)[0] / args.steps
     R = args.regions or n_regions(probe, args.steps)
+    if world > 1:
+        # every rank must time the same number of regions (the per-region times are reduced over ranks)
+        r_all = torch.tensor([R], dtype=torch.int64, device=dev)
+        dist.all_reduce(r_all, op=dist.ReduceOp.MAX)
+        R = int(r_all.item())
     with ClockSampler(physical_gpu_index(local)) as clocks:
         barrier()
         torch.cuda.profiler.start()   # a profiler attached with "--profile-from-start off" sees the timed region only

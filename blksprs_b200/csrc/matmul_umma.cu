@@ -24,18 +24,24 @@
 //                 each) per run and entry, releases the stage with tcgen05.commit, and hands a
 //                 finished accumulator group (the G accumulators of a panel, adjacent
 //                 tensor-memory columns) to the epilogue
-//   warps S+1..S+4 epilogue: tcgen05.ld the fp32 accumulators, add the bias row if there is one,
-//                 convert, write the output blocks in whole 32-byte sectors; blocks no step
-//                 touched are written as zeros (or the bias row)
+//   warps S+1..S+4 epilogue: tcgen05.ld the fp32 accumulators, hand the accumulator group back as
+//                 soon as the last of them is in registers, apply the epilogue variant (plain;
+//                 bias row added; or scale + block-local softmax: exp(s - row maximum) and the
+//                 (maximum, sum) pair of every row), convert, exchange words between lanes so
+//                 that neighbouring lanes hold neighbouring bytes of one output row, and store
+//                 whole 128-byte lines; blocks no step touched are written as zeros (the bias
+//                 row; ones in softmax mode)
 //
 // The panels are cut into small units that are handed out in order: a CTA starts with unit
 // blockIdx.x and then draws unit numbers from a global counter (or, without one, takes every
 // gridDim.x-th unit).  Producer 0 draws two units ahead and publishes the numbers through a
 // queue in shared memory, from which all roles of the CTA read the same sequence.
 //
-// Every wait is bounded (about one second): a wait that runs out records
+// Every mbarrier and queue wait is bounded (about one second): a wait that runs out records
 // BSP_ERR_DEVICE_TIMEOUT in the status word, all roles leave their loops, outstanding copies
 // and MMAs are drained with bounded waits, tensor memory is freed and the kernel returns.
+// (tcgen05.alloc itself blocks while CTAs of an earlier grid on the same SM still hold tensor
+// memory, and returns when they exit.)
 #include <float.h>
 
 #include <atomic>
