@@ -118,6 +118,64 @@ class _BlockSparseMatmul(torch.autograd.Function):
         return grad_x, grad_y, None, None, None, None
 
 
+# ---- registered ops ------------------------------------------------------------------------------
+# The reference registers its forward as ``torch.library.triton_op("blksprs::matmul_forward")`` with autograd
+# attached (blksprs/ops/matmul.py:70-75, 283-293).  The same positional schema is registered here under the
+# ``blksprs_b200`` namespace, for callers that address the op through ``torch.ops`` or want it inside a
+# ``torch.compile`` graph without a graph break (pre-built LUTs, validation off).  The ops are opaque to the
+# compiler; they find their plans through the layout tensors (library-owned cache, ``utils/tools.py``).  The eager
+# ``matmul`` wrapper keeps using the lighter ``autograd.Function`` above.
+
+@torch.library.custom_op("blksprs_b200::matmul_forward", mutates_args=(), device_types="cuda")
+def matmul_forward(x: Tensor, y: Tensor,
+                   sparsity_layout_x: Tensor, sparsity_reverse_lut_x: Tensor,
+                   sparsity_layout_y: Tensor, sparsity_reverse_lut_y: Tensor,
+                   sparsity_layout_o: Tensor, sparsity_lut_o: Tensor,
+                   sparsity_block_size: int, n_sparse_blocks: int) -> Tensor:
+    cache = matmul_build_layout_cache(None, sparsity_layout_x, sparsity_layout_y, sparsity_layout_o)
+    return cache[_PLANS].forward.run(x.contiguous(), y.contiguous(), sparsity_block_size)
+
+
+@matmul_forward.register_fake
+def _(x, y, sparsity_layout_x, sparsity_reverse_lut_x, sparsity_layout_y, sparsity_reverse_lut_y,
+      sparsity_layout_o, sparsity_lut_o, sparsity_block_size, n_sparse_blocks):
+    return x.new_empty((n_sparse_blocks, sparsity_block_size, sparsity_block_size))
+
+
+@torch.library.custom_op("blksprs_b200::matmul_backward", mutates_args=(), device_types="cuda")
+def matmul_backward(grad_output: Tensor, x: Tensor, y: Tensor, sparsity_layout_x: Tensor, sparsity_layout_y: Tensor,
+                    sparsity_layout_o: Tensor, sparsity_block_size: int) -> tuple[Tensor, Tensor]:
+    """dX = dO * Y^T on x's layout, dY = X^T * dO on y's layout (blksprs/ops/matmul.py:130-145)."""
+    cache = matmul_build_layout_cache(None, sparsity_layout_x, sparsity_layout_y, sparsity_layout_o)
+    plans: _MatmulPlans = cache[_PLANS]
+    x, y = x.contiguous(), y.contiguous()
+    _backward_plans(plans, cache["packed_indices_x"], cache["packed_indices_y"], x.size(0), y.size(0))
+    grad_output = grad_output.contiguous().to(x.dtype)
+    return (plans.grad_x.run(grad_output, y, sparsity_block_size),
+            plans.grad_y.run(x, grad_output, sparsity_block_size))
+
+
+@matmul_backward.register_fake
+def _(grad_output, x, y, sparsity_layout_x, sparsity_layout_y, sparsity_layout_o, sparsity_block_size):
+    return torch.empty_like(x), torch.empty_like(y)
+
+
+def _registered_setup_context(ctx, inputs, output):
+    x, y, sl_x, _, sl_y, _, sl_o, _, sparsity_block_size, _ = inputs
+    ctx.save_for_backward(x, y, sl_x, sl_y, sl_o)
+    ctx.sparsity_block_size = sparsity_block_size
+
+
+def _registered_backward(ctx, grad_output):
+    x, y, sl_x, sl_y, sl_o = ctx.saved_tensors
+    grad_x, grad_y = torch.ops.blksprs_b200.matmul_backward(grad_output, x, y, sl_x, sl_y, sl_o,
+                                                            ctx.sparsity_block_size)
+    return grad_x, grad_y, None, None, None, None, None, None, None, None
+
+
+matmul_forward.register_autograd(_registered_backward, setup_context=_registered_setup_context)
+
+
 def _validate_warm(x: Tensor, y: Tensor, plans: _MatmulPlans, sparsity_block_size: int) -> None:
     """The checks that depend on ``x`` and ``y`` (messages as in the full validation); everything that
     depends on the layouts alone was checked when this cache was built and the cache key pins the layouts."""
