@@ -713,12 +713,26 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 T* d0 = o + (int64_t)r0 * BS;
                                 T* d1 = d0 + 8 * BS;
                                 if constexpr (sizeof(T) == 4) {
-                                    // a thread's two adjacent columns are 8 bytes; the four threads of a quad
-                                    // fill one 32-byte sector
+                                    // fp32 data: a thread's two adjacent columns are 8 bytes.  Neighbouring lanes
+                                    // swap their pieces of two neighbouring column groups (even lanes keep group
+                                    // gq, odd lanes group gq + 1), so that every thread stores 16 bytes and a quad
+                                    // fills 64 contiguous bytes of each of the two groups' rows.
+                                    const bool odd = qd & 1;
 #pragma unroll
-                                    for (int gq = 0; gq < 8; ++gq) {
-                                        st_global_8B(d0 + 8 * gq + 2 * qd, v[4 * gq], v[4 * gq + 1]);
-                                        st_global_8B(d1 + 8 * gq + 2 * qd, v[4 * gq + 2], v[4 * gq + 3]);
+                                    for (int gq = 0; gq < 8; gq += 2) {
+                                        uint32_t ra[4], rb[4];
+#pragma unroll
+                                        for (int e = 0; e < 2; ++e) {
+                                            const uint32_t xa = __shfl_xor_sync(0xffffffffu, odd ? v[4 * gq + e] : v[4 * gq + 4 + e], 1);
+                                            const uint32_t xb = __shfl_xor_sync(0xffffffffu, odd ? v[4 * gq + 2 + e] : v[4 * gq + 6 + e], 1);
+                                            ra[e] = odd ? xa : v[4 * gq + e];
+                                            ra[2 + e] = odd ? v[4 * gq + 4 + e] : xa;
+                                            rb[e] = odd ? xb : v[4 * gq + 2 + e];
+                                            rb[2 + e] = odd ? v[4 * gq + 6 + e] : xb;
+                                        }
+                                        const int col = odd ? 8 * (gq + 1) + 2 * (qd - 1) : 8 * gq + 2 * qd;
+                                        st_global_16B(d0 + col, ra);
+                                        st_global_16B(d1 + col, rb);
                                     }
                                 } else {
                                     // 16-bit data: a thread's two columns are one 4-byte word, the four threads
@@ -817,18 +831,14 @@ matmul_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                         v[e] = __float_as_uint(ex);
                                     }
                                 }
-                                if (row_valid) {
-                                    // 32 fp32 columns = 128 bytes of the row: four 32-byte stores
-                                    T* dst = o + (int64_t)row * BS + c0;
+                                {
+                                    // (fp32 data, block size 128.)  lane = row; 32 fp32 columns are one 128-byte line of the row.  The same
+                                    // 8 x 8 exchange of 16-byte chunks as for 16-bit data: afterwards 8
+                                    // neighbouring lanes store one row's whole line per instruction.
+                                    octet_gather_chunks(v, lane);
+                                    T* obase = o + (int64_t)(wq * 32 + (lane & ~7)) * BS + c0 + (lane & 7) * 4;
 #pragma unroll
-                                    for (int i = 0; i < 4; ++i) {
-                                        uint32_t w8[8];
-#pragma unroll
-                                        for (int e = 0; e < 8; ++e)  // + 0: the vector store gets registers of its
-                                            // own (it cannot take the load's octet in place); -0 becomes +0
-                                            w8[e] = __float_as_uint(__uint_as_float(v[8 * i + e]) + 0.0f);
-                                        st_global_32B(dst + 8 * i, w8);
-                                    }
+                                    for (int i = 0; i < 8; ++i) st_global_16B(obase + (int64_t)i * BS, v + 4 * i);
                                 }
                             }
                             if constexpr (SOFTMAX) {

@@ -151,9 +151,6 @@ __device__ __forceinline__ void tc_ld16x64(uint32_t taddr, uint32_t* r) {
 __device__ __forceinline__ void st_global_16B(void* p, const uint32_t* u) {
     asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]) : "memory");
 }
-__device__ __forceinline__ void st_global_8B(void* p, uint32_t a, uint32_t b) {
-    asm volatile("st.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
-}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, sm_100 descriptor version 1.  Layout type 2 = 128-byte swizzle
