@@ -4,22 +4,26 @@
 // blksprs/ops/matmul.py:242), and any other (dtype, bs) when asked for by
 // BSP_KERNEL_MMA.
 //
-// Two kernels.
+// Three kernels.
 //
-// matmul_mma_stream_kernel (block sizes 16 and 32): persistent CTAs of four warps; every warp
-// works on its own.  A warp takes chunks of up to 32 consecutive output blocks; the pairs of those
-// blocks are one contiguous range of the pair list, which the warp streams through a ring of
-// cp.async stages of its own (one stage = the two operand blocks of a pair), several pairs ahead
-// and across output-block boundaries, with the pair records themselves fetched 32 at a time.
-// Block boundaries come from the offsets array.  No CTA-wide barrier exists in the loop; a
-// block's result goes from the accumulator fragments straight to global memory.
+// matmul_mma_direct_kernel (block sizes 16 and 32, except fp32 blocks of 32): persistent CTAs of
+// four warps; every warp works on its own and moves operand blocks from global memory straight into
+// the registers that feed mma.sync, without shared memory or barriers (see the comment above it).
+//
+// matmul_mma_stream_kernel (fp32 blocks of 32): the same warp-autonomous walk over chunks of up to
+// 32 consecutive output blocks, but with a ring of cp.async stages in shared memory per warp (one
+// stage = the two operand blocks of a pair), several pairs ahead and across output-block
+// boundaries, with the pair records fetched 32 at a time.
 //
 // matmul_mma_kernel (any block size; used for >= 64 when this family is asked for): one CTA
 // computes one TILE x TILE tile of one output block, double-buffered cp.async per (pair, k-chunk).
 //
-// Operand tiles are always copied in their global orientation; whether an operand is read
-// transposed (BSP_OP_NT / BSP_OP_TN) is decided when the fragments are read from shared memory
-// (ldmatrix[.trans] for 16-bit data, scalar loads for fp32).
+// In the first two a block's result goes from the accumulator fragments straight to global memory
+// and block boundaries come from the offsets array; no CTA-wide barrier exists in their loops.
+//
+// The two shared-memory kernels copy operand tiles in their global orientation; whether an operand
+// is read transposed (BSP_OP_NT / BSP_OP_TN) is decided when the fragments are read from shared
+// memory (ldmatrix[.trans] for 16-bit data, scalar loads for fp32).
 #include "common.cuh"
 
 namespace bsp {
@@ -253,10 +257,8 @@ matmul_mma_kernel(const T* __restrict__ a, int64_t n_a, const T* __restrict__ b,
 // ---- warp-autonomous streaming kernel for block sizes 16 and 32 ----------------------------
 
 template <typename T, int BS> struct StreamCfg {
-    // Ring depth per warp.  The loop is bound by instruction issue and by the latency of dependent
-    // mma.sync instructions on a block's few accumulators, not by memory latency (profiler: no
-    // long-scoreboard stalls at 3 warps per scheduler, issue slots 47 % used), so the ring is kept
-    // short to fit more warps per SM: 36 / 12 warps for 16-bit blocks of 16 / 32, 24 / 8 for fp32.
+    // Ring depth per warp, kept short to fit more warps per SM (fp32 blocks of 32, the one case this
+    // kernel serves: two stages of 8.5 KiB per warp, 12 warps per SM).
     static constexpr int kStages = sizeof(T) == 2 ? (BS == 16 ? 4 : 3) : (BS == 16 ? 3 : 2);
     static constexpr int kWarps = 4;
 };
@@ -508,24 +510,400 @@ static int launch_stream(const void* a, int64_t n_a, const void* b, int64_t n_b,
     return BSP_OK;
 }
 
+
+// ---- register-streaming kernel for block sizes 16 and 32 ------------------------------------
+//
+// Operand blocks go from global memory straight into the registers that feed mma.sync: no shared
+// memory, no barrier.  What makes that possible is that a product does not care in which order
+// its k terms are added, nor in which order its rows and columns are produced, as long as both
+// operands agree on k and the result is stored where it belongs.
+//
+// Every lane (g = lane / 4, t4 = lane % 4) reads BS / 8 "row vectors" of each operand block: a row
+// vector is the E = BS / 4 consecutive elements [E t4, E t4 + E) of one storage row, so four lanes
+// read one whole row and a warp-wide load reads eight whole rows.  Vector r of a lane comes from
+// row P(r) = E (g / 2) + 2 r + g % 2 ("permuted rows") or from row g + 8 r ("standard rows"); either
+// way a lane's vectors are a fixed distance apart.  Then
+//   * an operand stored with k along its rows (A of NN / NT, B of NT) already is an mma fragment
+//     under the k assignment "k-step s, register half h of lane t4 = elements E t4 + 4 s + 2 h, + 1"
+//     (16-bit data; E t4 + 2 s + h for tf32).  Its storage rows are m (n) indices: A uses standard
+//     rows (a warp-wide load is one contiguous run), B permuted ones, which makes column tile j of
+//     lane (g, t4) the output column E t4 + 2 j + {0, 1}: a lane's accumulators of one row are E
+//     consecutive output elements and are written as one vector;
+//   * a 16-bit operand stored with k along its columns (B of NN / TN, A of TN), read with permuted
+//     rows, becomes the same fragment, with the same k assignment and the same column (row)
+//     assignment, after one movmatrix (8 x 8 transposition across the warp) per register;
+//   * fp32 operands with k along the columns cannot be transposed that way; they are read with
+//     scalar loads in the standard fragment order (eight lanes = one 32-byte sector).
+// A warp keeps D pairs in flight in registers (D * BS^2 / 8 bytes per lane); the residency of many
+// warps per SM hides the rest of the latency.  On a product whose operands sit in L2 the kernel is
+// bound by the L1 data path (operand vectors, movmatrix and the record shuffles all pass through it).
+
+template <typename T, int BS> struct DirectCfg {
+    static constexpr int kDepth = sizeof(T) == 2 ? (BS == 16 ? 4 : 2) : (BS == 16 ? 2 : 1);
+    static constexpr int kWarps = 4;
+    // resident CTAs per SM the register allocation is held to
+    static constexpr int kMinCtas = sizeof(T) == 2 ? (BS == 16 ? 7 : 4) : (BS == 16 ? 6 : 3);
+};
+
+__device__ inline uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(x));
+    return d;
+}
+template <int N>
+__device__ inline void load_words(const char* p, uint32_t (&dst)[N]) {
+    static_assert(N == 2 || N == 4 || N == 8, "vector of 8, 16 or 32 bytes");
+    if constexpr (N == 2) {
+        const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+        dst[0] = v.x; dst[1] = v.y;
+    } else {
+#pragma unroll
+        for (int i = 0; i < N / 4; ++i) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(p) + i);
+            dst[4 * i] = v.x; dst[4 * i + 1] = v.y; dst[4 * i + 2] = v.z; dst[4 * i + 3] = v.w;
+        }
+    }
+}
+template <int N>
+__device__ inline void store_words(char* p, const uint32_t (&src)[N]) {
+    if constexpr (N == 2) {
+        *reinterpret_cast<uint2*>(p) = make_uint2(src[0], src[1]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < N / 4; ++i)
+            reinterpret_cast<uint4*>(p)[i] = make_uint4(src[4 * i], src[4 * i + 1], src[4 * i + 2], src[4 * i + 3]);
+    }
+}
+__device__ inline uint32_t pack2(__half, float x, float y) {
+    const __half2 h = __floats2half2_rn(x, y);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ inline uint32_t pack2(__nv_bfloat16, float x, float y) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <typename T, int BS, int OP>
+__global__ void __launch_bounds__(128, DirectCfg<T, BS>::kMinCtas)
+matmul_mma_direct_kernel(const T* __restrict__ a, int64_t n_a, const T* __restrict__ b, int64_t n_b,
+                         T* __restrict__ out, const int32_t* __restrict__ offsets,
+                         const int32_t* __restrict__ pairs, int n_out, int chunk,
+                         int32_t* __restrict__ status_word) {
+    constexpr bool K16 = Elem<T>::k16;
+    constexpr bool A_KROWS = (OP != BSP_OP_TN);  // A stored [m][k]
+    constexpr bool B_KROWS = (OP == BSP_OP_NT);  // B stored [n][k]
+    // 16-bit operands with k along the columns are transposed in registers ...
+    constexpr bool A_MOVM = K16 && !A_KROWS, B_MOVM = K16 && !B_KROWS;
+    // ... fp32 ones are read with scalar loads in the standard fragment order
+    constexpr bool A_SCALAR = !K16 && !A_KROWS, B_SCALAR = !K16 && !B_KROWS;
+    constexpr int D = DirectCfg<T, BS>::kDepth;
+    constexpr int E = BS / 4;                          // elements of a row vector
+    constexpr int R = BS / 8;                          // row vectors per lane and operand
+    constexpr int X = E * (int)sizeof(T) / 4;          // 32-bit registers per row vector
+    constexpr int MT = BS / 16, NT = BS / 8, KS = BS / (K16 ? 16 : 8);
+    constexpr int ROW_BYTES = BS * (int)sizeof(T);
+    constexpr int64_t BLK_BYTES = (int64_t)BS * ROW_BYTES;
+    // Rows of the row vectors.  Where the row index is an m or n index that no transposition ties to
+    // k, any assignment works, and "vector r = row g + 8 r" makes a warp-wide access one contiguous
+    // run of eight rows.  A's rows are of that kind when A has k along its rows (they become the
+    // result's rows); B's n rows (NT) are not, because the result's columns follow them.
+    constexpr bool A_PROWS = A_MOVM;
+    constexpr int A_VEC_STRIDE = (A_PROWS ? 2 : 8) * ROW_BYTES, B_VEC_STRIDE = 2 * ROW_BYTES;
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int total_warps = gridDim.x * DirectCfg<T, BS>::kWarps;
+    const int n_chunks = (n_out + chunk - 1) / chunk;
+    // byte offsets, inside a block, of this lane's row vector 0 with permuted and with standard rows ...
+    const int prow_off = (E * (g >> 1) + (g & 1)) * ROW_BYTES + E * t4 * (int)sizeof(T);
+    const int srow_off = g * ROW_BYTES + E * t4 * (int)sizeof(T);
+    // ... and of its first scalar element (fp32, k along the columns): row E t4, column g
+    const int sca_off = E * t4 * ROW_BYTES + g * 4;
+    const char* a_lane = reinterpret_cast<const char*>(a) + (A_SCALAR ? sca_off : A_PROWS ? prow_off : srow_off);
+    const char* b_lane = reinterpret_cast<const char*>(b) + (B_SCALAR ? sca_off : prow_off);
+    // the result: row vector r of this lane, in the rows A's assignment gives it
+    char* out_lane = reinterpret_cast<char*>(out) + (A_PROWS ? prow_off : srow_off);
+    // range limits as 32-bit values (a masked index is below 2^30, a negative one becomes huge)
+    const uint32_t lim_a = (uint32_t)(n_a < 0x40000000LL ? n_a : 0x40000000LL);
+    const uint32_t lim_b = (uint32_t)(n_b < 0x7fffffffLL ? n_b : 0x7fffffffLL);
+
+    float acc[MT][NT][4];
+    auto clear_acc = [&]() {
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) acc[i][j][r] = 0.f;
+    };
+    auto write_block = [&](int64_t p) {
+        char* o = out_lane + p * BLK_BYTES;
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int r = 2 * i + u;
+                if constexpr (!B_SCALAR) {
+                    // E consecutive elements of one row
+                    uint32_t w[X];
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        if constexpr (K16) {
+                            w[j] = pack2(T(), acc[i][j][2 * u], acc[i][j][2 * u + 1]);
+                        } else {
+                            w[2 * j] = __float_as_uint(acc[i][j][2 * u]);
+                            w[2 * j + 1] = __float_as_uint(acc[i][j][2 * u + 1]);
+                        }
+                    }
+                    store_words<X>(o + r * A_VEC_STRIDE, w);
+                } else {
+                    // standard columns: two elements per column tile (out_lane points at column E t4 of the row)
+#pragma unroll
+                    for (int j = 0; j < NT; ++j)
+                        *reinterpret_cast<float2*>(o + r * A_VEC_STRIDE + (8 * j + 2 * t4 - E * t4) * 4) =
+                            make_float2(acc[i][j][2 * u], acc[i][j][2 * u + 1]);
+                }
+            }
+    };
+
+    uint32_t ra[D][R][X], rb[D][R][X];
+    auto load_operand = [&](const char* blk, const bool scalar, const int stride, uint32_t (&dst)[R][X]) {
+        if (!scalar) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) load_words<X>(blk + r * stride, dst[r]);
+        } else {
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int y = 0; y < X; ++y)
+                    dst[r][y] = __ldg(reinterpret_cast<const uint32_t*>(blk + y * ROW_BYTES + 32 * r));
+        }
+    };
+    // multiplies the pair held in a slot into the accumulators
+    auto multiply = [&](uint32_t (&fa)[R][X], uint32_t (&fb)[R][X]) {
+        if constexpr (A_MOVM) {
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int x = 0; x < X; ++x) fa[r][x] = movmatrix_trans(fa[r][x]);
+        }
+        if constexpr (B_MOVM) {
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int x = 0; x < X; ++x) fb[r][x] = movmatrix_trans(fb[r][x]);
+        }
+#pragma unroll
+        for (int s = 0; s < KS; ++s) {
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+                uint32_t af[4];
+                if constexpr (A_MOVM) {
+                    af[0] = fa[2 * s][2 * i]; af[1] = fa[2 * s][2 * i + 1];
+                    af[2] = fa[2 * s + 1][2 * i]; af[3] = fa[2 * s + 1][2 * i + 1];
+                } else {
+                    af[0] = fa[2 * i][2 * s]; af[1] = fa[2 * i + 1][2 * s];
+                    af[2] = fa[2 * i][2 * s + 1]; af[3] = fa[2 * i + 1][2 * s + 1];
+                }
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    uint32_t bf[2];
+                    if constexpr (B_MOVM) {
+                        bf[0] = fb[2 * s][j]; bf[1] = fb[2 * s + 1][j];
+                    } else {
+                        bf[0] = fb[j][2 * s]; bf[1] = fb[j][2 * s + 1];
+                    }
+                    Elem<T>::mma(acc[i][j], af, bf);
+                }
+            }
+        }
+    };
+    // requests the operand blocks of a pair record into a slot.  Indices outside the operands are
+    // reported in the status word and replaced by block 0 (which exists whenever a pair does).
+    auto request = [&](const int2& win, int l, uint32_t (&fa)[R][X], uint32_t (&fb)[R][X]) {
+        uint32_t ia = (uint32_t)__shfl_sync(0xffffffffu, win.x, l) & 0x3fffffffu;  // bit 30: a block's last pair
+        uint32_t ib = (uint32_t)__shfl_sync(0xffffffffu, win.y, l);
+        if (ia >= lim_a || ib >= lim_b) {
+            if (status_word && lane == 0) *status_word = BSP_ERR_DEVICE_RANGE;
+            ia = ib = 0;
+        }
+        load_operand(a_lane + (uint64_t)ia * (uint64_t)BLK_BYTES, A_SCALAR, A_VEC_STRIDE, fa);
+        load_operand(b_lane + (uint64_t)ib * (uint64_t)BLK_BYTES, B_SCALAR, B_VEC_STRIDE, fb);
+    };
+
+    // A chunk: up to 32 consecutive output blocks, whose pairs are one contiguous range of the pair
+    // list.  Lane l holds the offset of the chunk's block l; the range's end is held by all.
+    struct Chunk { int p0, nb, my_off, q_end; };
+    auto fetch_chunk = [&](int c) -> Chunk {
+        Chunk k = {0, 0, 0, 0};
+        if (c < n_chunks) {
+            k.p0 = c * chunk;
+            k.nb = min(chunk, n_out - k.p0);
+            k.my_off = offsets[k.p0 + min(lane, k.nb)];
+            k.q_end = offsets[k.p0 + k.nb];
+        }
+        return k;
+    };
+    // pair records of a chunk, 32 at a time: lane l of window w holds the record of stream position 32 w + l
+    auto load_window = [&](int q_begin, int q_end, int w) -> int2 {
+        const int q = q_begin + w * 32 + lane;
+        if (q < q_end) return *reinterpret_cast<const int2*>(pairs + 2 * (int64_t)q);
+        return make_int2(0, 0);
+    };
+    // without operand blocks there is nothing to multiply: every block is written as zeros
+    const bool have_operands = n_a > 0 && n_b > 0;
+
+    int c = blockIdx.x * DirectCfg<T, BS>::kWarps + warp;
+    Chunk cur = fetch_chunk(c);
+    int q_begin = __shfl_sync(0xffffffffu, cur.my_off, 0);
+    int2 win = load_window(q_begin, cur.q_end, 0);
+    int n_pairs = have_operands ? cur.q_end - q_begin : 0;
+    // The pair stream of a chunk is walked by request position t: position t is requested into slot
+    // t % D right after position t - D, which occupied that slot, has been multiplied; the walk runs
+    // D positions past the stream's end.  The first D positions of a chunk are requested before the
+    // chunk begins (here, and at the end of the chunk before it).
+#pragma unroll
+    for (int d = 0; d < D; ++d)
+        if (d < n_pairs) request(win, d, ra[d], rb[d]);
+
+    while (c < n_chunks) {
+        // the next chunk's offsets travel while this chunk is worked on
+        const Chunk nxt = fetch_chunk(c + total_warps);
+        int2 nxt_win = make_int2(0, 0);
+        int nxt_q_begin = 0;
+        bool nxt_win_loaded = false;
+        auto load_next_window = [&]() {
+            nxt_q_begin = __shfl_sync(0xffffffffu, nxt.my_off, 0);
+            nxt_win = load_window(nxt_q_begin, nxt.q_end, 0);
+            nxt_win_loaded = true;
+        };
+
+        clear_acc();
+        int blk = 0;  // current block, relative to p0
+        // stream position at which block `bl` ends
+        auto block_end = [&](int bl) {
+            const int e = __shfl_sync(0xffffffffu, cur.my_off, min(bl + 1, 31));
+            return bl + 1 >= cur.nb ? n_pairs : e - q_begin;
+        };
+        int blk_end = block_end(0);
+        // one position; CHECKED = false promises that t - D and t are inside the stream
+        auto step = [&](const bool CHECKED, int t, uint32_t (&fa)[R][X], uint32_t (&fb)[R][X]) {
+            const int s = t - D;
+            if (!CHECKED || s < n_pairs) {
+                // blocks that end before this pair (the previous pair's block, and empty ones) are written
+                while (s == blk_end) {
+                    write_block(cur.p0 + blk);
+                    clear_acc();
+                    ++blk;
+                    blk_end = block_end(blk);
+                }
+                multiply(fa, fb);
+            }
+            if (!CHECKED || t < n_pairs) request(win, t & 31, fa, fb);
+        };
+        const int n_windows = (n_pairs + D + 31) >> 5;
+        for (int w = 0; w < n_windows; ++w) {
+            const int2 win_next = load_window(q_begin, cur.q_end, w + 1);
+            // the next chunk's first records are asked for one window before they are needed
+            if (w == n_windows - 1) load_next_window();
+            const int base = w << 5;
+            if (w > 0 && base + 32 <= n_pairs) {
+#pragma unroll 1
+                for (int tt = 0; tt < 32; tt += D) {
+#pragma unroll
+                    for (int d = 0; d < D; ++d) step(false, base + tt + d, ra[d], rb[d]);
+                }
+            } else {
+#pragma unroll 1
+                for (int tt = (w == 0 ? D : 0); tt < 32; tt += D) {
+#pragma unroll
+                    for (int d = 0; d < D; ++d) step(true, base + tt + d, ra[d], rb[d]);
+                }
+            }
+            win = win_next;
+        }
+        if (!nxt_win_loaded) load_next_window();
+        // all slots are free: the next chunk's first positions are requested before this chunk's last
+        // blocks are written
+        const int nxt_pairs = have_operands ? nxt.q_end - nxt_q_begin : 0;
+#pragma unroll
+        for (int d = 0; d < D; ++d)
+            if (d < nxt_pairs) request(nxt_win, d, ra[d], rb[d]);
+        // the chunk's remaining blocks: the last one with pairs, and empty ones behind it
+        while (blk < cur.nb) {
+            write_block(cur.p0 + blk);
+            clear_acc();
+            ++blk;
+        }
+        cur = nxt;
+        win = nxt_win;
+        q_begin = nxt_q_begin;
+        n_pairs = nxt_pairs;
+        c += total_warps;
+    }
+}
+
+template <typename T, int BS, int OP>
+static int launch_direct(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out, int64_t n_out,
+                         const int32_t* offsets, const int32_t* pairs, int32_t* status_word, cudaStream_t stream) {
+    constexpr int W = DirectCfg<T, BS>::kWarps;
+    auto kern = matmul_mma_direct_kernel<T, BS, OP>;
+    // per device, looked up once: the SM count and the resident CTAs per SM
+    static int cached_sms[64] = {0}, cached_per_sm[64] = {0};
+    int dev = 0;
+    BSP_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return BSP_ERR_UNSUPPORTED;
+    if (cached_sms[dev] == 0) {
+        int n_sm = 0, n_cta = 0;
+        BSP_CUDA_TRY(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+        BSP_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n_cta, kern, 32 * W, 0));
+        cached_per_sm[dev] = n_cta < 1 ? 1 : n_cta;
+        cached_sms[dev] = n_sm;
+    }
+    const int sms = cached_sms[dev], per_sm = cached_per_sm[dev];
+    // chunks of consecutive output blocks per warp visit: as large as the block count allows while
+    // every resident warp still gets several chunks (small problems: one block per warp)
+    const int64_t warps = (int64_t)sms * per_sm * W;
+    int64_t chunk = n_out / (warps * 4);
+    chunk = chunk < 1 ? 1 : (chunk > 32 ? 32 : chunk);
+    const int64_t n_chunks = (n_out + chunk - 1) / chunk;
+    int64_t ctas = (n_chunks + W - 1) / W;
+    if (ctas > (int64_t)sms * per_sm) ctas = (int64_t)sms * per_sm;
+    kern<<<(unsigned)ctas, 32 * W, 0, stream>>>((const T*)a, n_a, (const T*)b, n_b, (T*)out, offsets, pairs,
+                                                (int)n_out, (int)chunk, status_word);
+    BSP_LAUNCH_CHECK();
+    return BSP_OK;
+}
+
+// Block sizes 16 and 32: the register-streaming kernel, except for fp32 blocks of 32, whose 8 KiB per
+// pair leave too few pairs in flight in registers (the shared-memory ring holds twice as many).
+template <typename T, int BS, int OP>
+static int launch_small(const void* a, int64_t n_a, const void* b, int64_t n_b, void* out, int64_t n_out,
+                        const int32_t* offsets, const int32_t* pairs, int32_t* status_word, cudaStream_t stream) {
+    if constexpr (sizeof(T) == 4 && BS == 32)
+        return launch_stream<T, BS, OP>(a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+    else
+        return launch_direct<T, BS, OP>(a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+}
+
 template <typename T, int BS>
-static int launch_stream_op(int op, const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
-                            int64_t n_out, const int32_t* offsets, const int32_t* pairs, int32_t* status_word,
-                            cudaStream_t stream) {
+static int launch_small_op(int op, const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
+                           int64_t n_out, const int32_t* offsets, const int32_t* pairs, int32_t* status_word,
+                           cudaStream_t stream) {
     switch (op) {
-        case BSP_OP_NN: return launch_stream<T, BS, BSP_OP_NN>(a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
-        case BSP_OP_NT: return launch_stream<T, BS, BSP_OP_NT>(a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
-        case BSP_OP_TN: return launch_stream<T, BS, BSP_OP_TN>(a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+        case BSP_OP_NN: return launch_small<T, BS, BSP_OP_NN>(a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+        case BSP_OP_NT: return launch_small<T, BS, BSP_OP_NT>(a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+        case BSP_OP_TN: return launch_small<T, BS, BSP_OP_TN>(a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
         default: return BSP_ERR_INVALID_ARG;
     }
 }
 
 template <typename T>
-static int launch_stream_bs(int bs, int op, const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
-                            int64_t n_out, const int32_t* offsets, const int32_t* pairs, int32_t* status_word,
-                            cudaStream_t stream) {
-    if (bs == 16) return launch_stream_op<T, 16>(op, a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
-    return launch_stream_op<T, 32>(op, a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+static int launch_small_bs(int bs, int op, const void* a, int64_t n_a, const void* b, int64_t n_b, void* out,
+                           int64_t n_out, const int32_t* offsets, const int32_t* pairs, int32_t* status_word,
+                           cudaStream_t stream) {
+    if (bs == 16) return launch_small_op<T, 16>(op, a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+    return launch_small_op<T, 32>(op, a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
 }
 
 template <typename T, int TILE, int OP>
@@ -579,9 +957,9 @@ int launch_matmul_mma(const void* a, int64_t n_a, const void* b, int64_t n_b, vo
     if (n_out > 0x7fffffffLL) return BSP_ERR_UNSUPPORTED;
     if (bs == 16 || bs == 32) {
         switch (dtype) {
-            case BSP_F16: return launch_stream_bs<__half>(bs, op, a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
-            case BSP_BF16: return launch_stream_bs<__nv_bfloat16>(bs, op, a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
-            case BSP_F32: return launch_stream_bs<float>(bs, op, a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+            case BSP_F16: return launch_small_bs<__half>(bs, op, a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+            case BSP_BF16: return launch_small_bs<__nv_bfloat16>(bs, op, a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
+            case BSP_F32: return launch_small_bs<float>(bs, op, a, n_a, b, n_b, out, n_out, offsets, pairs, status_word, stream);
             default: return BSP_ERR_UNSUPPORTED;
         }
     }
