@@ -14,7 +14,7 @@ import torch
 from torch import Tensor
 
 from .. import _cabi
-from ..plan import Product
+from ..plan import Product, prepare_products
 from ..utils.blksprs_tensor import BlksprsTensor
 from ..utils.tools import build_layout_indices, build_packed_indices, cast_for_autocast, count_active_blocks, \
     finalize_layout_cache, implicit_layout_cache, layout_cache_is_current, prepare_layout_cache
@@ -238,11 +238,17 @@ def _matmul_eager(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_ou
             # validate_sparsity has just confirmed the block counts against the layouts
             plans.n_x, plans.n_y = x.size(0), y.size(0)
             plans.layouts_validated = True
+        requests = [(plans.forward, sparsity_block_size, x.dtype, x.size(0), y.size(0))]
         if torch.is_grad_enabled() and (x.requires_grad or y.requires_grad):
             # a training step will need them: build the plans of dX and dY with the forward plan, so that all
             # cold-path device reads of a layout triple happen in its first forward call
             _backward_plans(plans, layout_cache["packed_indices_x"], layout_cache["packed_indices_y"], x.size(0),
                             y.size(0))
+            n_o = plans.forward.n_out
+            requests += [(plans.grad_x, sparsity_block_size, x.dtype, n_o, y.size(0)),
+                         (plans.grad_y, sparsity_block_size, x.dtype, x.size(0), n_o)]
+        # the sizes of all plans this call (and its backward) will use arrive in one device->host copy
+        prepare_products(requests)
 
     out = _BlockSparseMatmul.apply(x, y, layout_cache["packed_indices_x"], layout_cache["packed_indices_y"],
                                    plans, sparsity_block_size)

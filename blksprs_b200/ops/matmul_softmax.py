@@ -60,7 +60,7 @@ def _softmax_rows(scores: Tensor, plans: _MatmulPlans, bs: int) -> Tensor:
 
 def _forward(x: Tensor, y: Tensor, plans: _MatmulPlans, bs: int, scale: float, out_dtype: torch.dtype) -> Tensor:
     product = plans.forward
-    n_out = product.pair.n_out
+    n_out = product.n_out
     device = x.device
     if n_out == 0:
         return torch.empty((0, bs, bs), dtype=out_dtype, device=device)

@@ -9,9 +9,10 @@ Pair plan (``bsp_plan_*``; consumed by the mma.sync kernel, and the yardstick fo
 ``offsets`` int32 ``(n_out + 1)`` CSR offsets per output block, ``pairs`` int32 ``(total, 2)``
 (a_block, b_block), inner index ascending.
 
-Step plan (``bsp_panel_*``; consumed by the tcgen05 kernel): output blocks of one output row are
-grouped into panels of ``width`` (1 or 2); a step is one inner index whose A block exists and that
-hits at least one of the panel's B blocks.  ``unit_panel`` / ``unit_step`` cut the panels into
+Step plan (``bsp_panel_*``; consumed by the tcgen05 kernel): every ``width`` (1 or 2) consecutive
+output blocks form a panel; a step is one inner index whose A block exists and that hits at least
+one of the panel's B blocks (the blocks of a panel that share an output row share their A blocks; a
+panel that runs across the end of a row is walked row by row).  ``unit_panel`` / ``unit_step`` cut the panels into
 contiguous units of equal cost that the persistent CTAs take in order — drawn from a counter
 (``SCHEDULE = "dynamic"``, small units) or round-robin (``"static"``, larger units) — so that all
 SMs work on neighbouring output rows (same batch, same operand blocks in L2) at the same time.
@@ -94,9 +95,26 @@ class PairPlan:
     pairs: Tensor
 
 
-def build_pair_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor,
-                    R: int, K: int, C: int) -> PairPlan:
-    """Builds the pair plan of one product; one device->host read (the total pair count)."""
+@dataclass
+class _Counted:
+    """The device half of a plan whose sizes the host has not read yet: per-block (per-panel)
+    counts and their offsets are on the device, ``totals`` (int64: the total, and for a step plan
+    the largest panel) waits to be read.  ``resolve_counts`` reads the totals of any number of these
+    in one device->host copy."""
+    width: int                      # 0 = pair plan, 1 / 2 = step plan of that panel width
+    walk: tuple
+    n_slots: int                    # output blocks (pair plan) or panels (step plan)
+    offsets: Tensor
+    totals: Tensor
+    panel_first: Tensor | None = None
+    touched: Tensor | None = None
+    total: int | None = None
+    largest: int | None = None
+    pairs: int | None = None        # (A block, B block) pairs the plan stands for
+
+
+def count_pairs(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor, R: int, K: int, C: int) -> _Counted:
+    """Counts the pairs of every output block and scans them; no device->host read."""
     device = lut_out.device
     n_out = lut_out.size(0)
     (a_sb, a_sr, a_st), (b_sb, b_st, b_sc), T = _walk_strides(op, R, K, C)
@@ -108,19 +126,50 @@ def build_pair_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor
         total = torch.empty(1, dtype=torch.int64, device=device)
         ws_bytes = lib.bsp_plan_workspace_bytes(n_out)
         ws = torch.empty(ws_bytes // 8, dtype=torch.int64, device=device)
-        _cabi.check(lib.bsp_plan_count(_cabi.ptr(lut_out), n_out, _cabi.ptr(packed_a), a_sb, a_sr, a_st,
-                                       _cabi.ptr(packed_b), b_sb, b_st, b_sc, T, _cabi.ptr(counts), stream),
-                    "bsp_plan_count")
+        walk = (_cabi.ptr(lut_out), n_out, _cabi.ptr(packed_a), a_sb, a_sr, a_st, _cabi.ptr(packed_b), b_sb, b_st,
+                b_sc, T)
+        _cabi.check(lib.bsp_plan_count(*walk, _cabi.ptr(counts), stream), "bsp_plan_count")
         _cabi.check(lib.bsp_plan_offsets(_cabi.ptr(counts), n_out, _cabi.ptr(offsets), _cabi.ptr(total),
                                          _cabi.ptr(ws), ws_bytes, stream), "bsp_plan_offsets")
-        n_pairs = read_with_status(total, device)[0]
-        if n_pairs > 2_147_483_647:
-            raise ValueError("blksprs_b200: pair plan exceeds 2^31-1 block pairs")
+    return _Counted(0, walk, n_out, offsets, total)
+
+
+def finish_pair_plan(op: int, counted: _Counted) -> PairPlan:
+    """Allocates and fills the pair list of a counted (and resolved) pair plan."""
+    n_pairs = counted.total
+    if n_pairs > 2_147_483_647:
+        raise ValueError("blksprs_b200: pair plan exceeds 2^31-1 block pairs")
+    device = counted.offsets.device
+    with torch.cuda.device(device):
         pairs = torch.empty((max(n_pairs, 1), 2), dtype=torch.int32, device=device)
-        _cabi.check(lib.bsp_plan_fill(_cabi.ptr(lut_out), n_out, _cabi.ptr(packed_a), a_sb, a_sr, a_st,
-                                      _cabi.ptr(packed_b), b_sb, b_st, b_sc, T, _cabi.ptr(offsets),
-                                      _cabi.ptr(pairs), stream), "bsp_plan_fill")
-    return PairPlan(op, n_out, n_pairs, offsets, pairs)
+        _cabi.check(_cabi.lib().bsp_plan_fill(*counted.walk, _cabi.ptr(counted.offsets), _cabi.ptr(pairs),
+                                              _cabi.stream_handle(device)), "bsp_plan_fill")
+    return PairPlan(op, counted.n_slots, n_pairs, counted.offsets, pairs)
+
+
+def resolve_counts(pending: list[_Counted]) -> None:
+    """Reads the totals of all ``pending`` plans (of one device) in a single device->host copy."""
+    pending = [c for c in pending if c.total is None]
+    if not pending:
+        return
+    device = pending[0].totals.device
+    values = read_with_status(torch.cat([c.totals for c in pending]), device)
+    at = 0
+    for c in pending:
+        c.total = values[at]
+        if c.totals.numel() > 1:
+            c.largest, c.pairs = values[at + 1], values[at + 2]
+        else:
+            c.pairs = c.total
+        at += c.totals.numel()
+
+
+def build_pair_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor,
+                    R: int, K: int, C: int) -> PairPlan:
+    """Builds the pair plan of one product; one device->host read (the total pair count)."""
+    counted = count_pairs(op, lut_out, packed_a, packed_b, R, K, C)
+    resolve_counts([counted])
+    return finish_pair_plan(op, counted)
 
 
 @dataclass
@@ -178,50 +227,49 @@ class StepPlan:
 SCHED_POOL_PAIRS = 64
 
 
-def build_step_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor, R: int, K: int, C: int,
-                    width: int, n_ctas: int, bs: int = 64) -> StepPlan:
-    """Groups the output blocks of every output row into panels of ``width``, lists each panel's
-    steps and cuts the panels into units; one device->host read (the total step count)."""
+def count_steps(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor, R: int, K: int, C: int,
+                width: int) -> _Counted:
+    """Groups the output blocks into panels of ``width`` consecutive blocks (the walk splits a panel
+    that runs across the end of a layout row into its rows), counts each panel's steps and scans
+    them; no device->host read."""
     device = lut_out.device
     n_out = lut_out.size(0)
     (a_sb, a_sr, a_st), (b_sb, b_st, b_sc), T = _walk_strides(op, R, K, C)
     lib = _cabi.lib()
     with torch.cuda.device(device):
         stream = _cabi.stream_handle(device)
-        if width == 1:
-            panel_first = torch.arange(n_out + 1, dtype=torch.int32, device=device)
-            n_panels = n_out
-        else:
-            # position of every output block inside its (batch, row) run, modulo the panel width
-            idx = torch.arange(n_out, device=device)
-            new_row = torch.ones(n_out, dtype=torch.bool, device=device)
-            if n_out > 1:
-                new_row[1:] = (lut_out[1:, 0] != lut_out[:-1, 0]) | (lut_out[1:, 1] != lut_out[:-1, 1])
-            row_first = torch.cummax(torch.where(new_row, idx, torch.zeros_like(idx)), 0).values
-            starts = torch.nonzero((idx - row_first) % width == 0).flatten()
-            n_panels = starts.numel()
-            panel_first = torch.empty(n_panels + 1, dtype=torch.int32, device=device)
-            panel_first[:n_panels] = starts
+        n_panels = -(-n_out // width)
+        panel_first = torch.arange(0, (n_panels + 1) * width, width, dtype=torch.int32, device=device)
+        if n_panels:
             panel_first[n_panels] = n_out
         counts = torch.empty(max(n_panels, 1), dtype=torch.int32, device=device)
         touched = torch.empty(max(n_panels, 1), dtype=torch.int32, device=device)
         offsets = torch.empty(n_panels + 1, dtype=torch.int32, device=device)
-        total = torch.empty(1, dtype=torch.int64, device=device)
+        # total steps (from the scan), largest panel and pair count (from the counting kernel)
+        totals = torch.zeros(3, dtype=torch.int64, device=device)
         ws_bytes = lib.bsp_plan_workspace_bytes(n_panels)
         ws = torch.empty(ws_bytes // 8, dtype=torch.int64, device=device)
         walk = (_cabi.ptr(lut_out), _cabi.ptr(panel_first), n_panels, _cabi.ptr(packed_a), a_sb, a_sr, a_st,
                 _cabi.ptr(packed_b), b_sb, b_st, b_sc, T)
-        _cabi.check(lib.bsp_panel_count(*walk, _cabi.ptr(counts), _cabi.ptr(touched), stream), "bsp_panel_count")
-        _cabi.check(lib.bsp_plan_offsets(_cabi.ptr(counts), n_panels, _cabi.ptr(offsets), _cabi.ptr(total),
+        _cabi.check(lib.bsp_panel_count(*walk, _cabi.ptr(counts), _cabi.ptr(touched), totals.data_ptr() + 8, stream),
+                    "bsp_panel_count")
+        _cabi.check(lib.bsp_plan_offsets(_cabi.ptr(counts), n_panels, _cabi.ptr(offsets), _cabi.ptr(totals),
                                          _cabi.ptr(ws), ws_bytes, stream), "bsp_plan_offsets")
-        largest = counts[:n_panels].max().to(torch.int64).reshape(1) if n_panels else total
-        n_steps, max_panel_steps = read_with_status(torch.cat([total, largest]), device)
-        if n_steps > 2_147_483_647 // 8:
-            raise ValueError("blksprs_b200: step plan too large")
+    return _Counted(width, walk, n_panels, offsets, totals, panel_first, touched)
+
+
+def finish_step_plan(op: int, n_out: int, counted: _Counted, n_ctas: int, bs: int) -> StepPlan:
+    """Lists the steps of a counted (and resolved) step plan and cuts its panels into units."""
+    width, n_panels, n_steps, max_panel_steps = counted.width, counted.n_slots, counted.total, counted.largest
+    if n_steps > 2_147_483_647 // 8:
+        raise ValueError("blksprs_b200: step plan too large")
+    offsets = counted.offsets
+    device = offsets.device
+    lib = _cabi.lib()
+    with torch.cuda.device(device):
+        stream = _cabi.stream_handle(device)
         steps = torch.empty((max(n_steps, 1), 8), dtype=torch.int32, device=device)
-        _cabi.check(lib.bsp_panel_fill(*walk, _cabi.ptr(offsets), _cabi.ptr(steps), stream), "bsp_panel_fill")
-        # units: every CTA gets the same number of equal-cost units; a unit is several times the
-        # heaviest panel, so that indivisible panels cannot unbalance the CTAs
+        _cabi.check(lib.bsp_panel_fill(*counted.walk, _cabi.ptr(offsets), _cabi.ptr(steps), stream), "bsp_panel_fill")
         cost = n_steps + BLOCK_COST * width * n_panels
         heaviest = max_panel_steps + BLOCK_COST * width
         # static round-robin: a unit is several times the heaviest panel, so that indivisible
@@ -241,10 +289,19 @@ def build_step_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor
         _cabi.check(lib.bsp_plan_schedule(_cabi.ptr(offsets), n_panels, BLOCK_COST * width, n_units,
                                           _cabi.ptr(unit_panel), stream), "bsp_plan_schedule")
         unit_step = offsets[unit_panel.long()].contiguous()
-        plan = StepPlan(op, n_out, n_panels, n_steps, width, panel_first, offsets, steps, touched, unit_panel,
-                        unit_step, n_units, SCHEDULE == "dynamic")
+        plan = StepPlan(op, n_out, n_panels, n_steps, width, counted.panel_first, offsets, steps, counted.touched,
+                        unit_panel, unit_step, n_units, SCHEDULE == "dynamic")
         plan.__dict__["_sched_pool"] = torch.zeros(2 * SCHED_POOL_PAIRS, dtype=torch.int32, device=device)
     return plan
+
+
+def build_step_plan(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor, R: int, K: int, C: int,
+                    width: int, n_ctas: int, bs: int = 64) -> StepPlan:
+    """Counts, reads (one device->host read: the total step count and the largest panel) and lists the
+    steps of one product for panels of ``width`` blocks."""
+    counted = count_steps(op, lut_out, packed_a, packed_b, R, K, C, width)
+    resolve_counts([counted])
+    return finish_step_plan(op, lut_out.size(0), counted, n_ctas, bs)
 
 
 _status_words: dict[torch.device, Tensor] = {}
@@ -323,39 +380,79 @@ def run_step_plan(plan: StepPlan, a: Tensor, b: Tensor, bs: int, bias: Tensor | 
 
 
 class Product:
-    """One block-sparse product (forward, dX or dY) of a layout triple: its pair plan and, built on
-    first use with block size 64 / 128, its step plans."""
+    """One block-sparse product (forward, dX or dY) of a layout triple.  Its plans are built when a
+    launch first needs them: the pair plan for the mma.sync kernels, step plans for the tcgen05
+    kernel (block size 64 / 128).  Building is split into a counting half without device->host read
+    and a listing half that needs the totals, so that everything a call needs — of all three products
+    of a training step — is read in one copy (``prepare_products``)."""
 
     def __init__(self, op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor, R: int, K: int, C: int):
         self.op, self.dims = op, (R, K, C)
         self.lut_out, self.packed_a, self.packed_b = lut_out, packed_a, packed_b
-        self.pair = build_pair_plan(op, lut_out, packed_a, packed_b, R, K, C)
+        self.n_out = lut_out.size(0)
+        self._counted: dict[int, _Counted] = {}     # 0 = pair plan, 1 / 2 = step plan of that width
+        self._pair: PairPlan | None = None
         self._steps: dict[tuple[int, int], StepPlan] = {}
+
+    def _count(self, widths) -> list[_Counted]:
+        """Launches the counting half of the plans in ``widths`` that are not counted yet; returns
+        those whose totals still have to be read."""
+        for w in widths:
+            if w not in self._counted:
+                args = (self.op, self.lut_out, self.packed_a, self.packed_b, *self.dims)
+                self._counted[w] = count_pairs(*args) if w == 0 else count_steps(*args, w)
+        return [self._counted[w] for w in widths if self._counted[w].total is None]
+
+    def _needed(self, bs: int, dtype: torch.dtype, n_a: int, n_b: int) -> tuple[int, ...]:
+        """Which plans a launch may consult under the current kernel selection."""
+        if (_kernel_choice == "mma" or bs not in (64, 128) or n_a == 0 or n_b == 0 or self.n_out == 0
+                or dtype not in (torch.float16, torch.bfloat16, torch.float32)):
+            return (0,)
+        if _kernel_choice == "umma":
+            return (1,)
+        if _kernel_choice == "panel":
+            return (2,)
+        # automatic: the two-block panels are counted first; their walk also yields the pair count the
+        # choice needs (``choose`` counts the single-block plan only when it picks that one)
+        return (2,) if bs in PANEL_AUTO_BLOCK_SIZES else (1,)
+
+    @property
+    def pair(self) -> PairPlan:
+        if self._pair is None:
+            resolve_counts(self._count((0,)))
+            self._pair = finish_pair_plan(self.op, self._counted[0])
+        return self._pair
 
     def step_plan(self, bs: int, dtype: torch.dtype, width: int) -> StepPlan:
         key = (bs, width)
         if key not in self._steps:
+            resolve_counts(self._count((width,)))
             n_ctas = _cabi.lib().bsp_umma_num_ctas(_cabi.DATA_DTYPE_CODES[dtype], bs, width)
-            self._steps[key] = build_step_plan(self.op, self.lut_out, self.packed_a, self.packed_b, *self.dims,
-                                               width, n_ctas, bs)
+            self._steps[key] = finish_step_plan(self.op, self.n_out, self._counted[width], n_ctas, bs)
         return self._steps[key]
 
     def choose(self, bs: int, dtype: torch.dtype, n_a: int, n_b: int) -> tuple[str, int]:
         """(kernel, panel width) for a launch under the current kernel selection."""
-        tensor_core_path = (dtype in (torch.float16, torch.bfloat16, torch.float32) and bs in (64, 128)
-                            and n_a > 0 and n_b > 0
-                            and self.pair.n_out > 0 and self.pair.n_pairs > 0)
-        if _kernel_choice == "mma" or not tensor_core_path:
+        needed = self._needed(bs, dtype, n_a, n_b)
+        if needed == (0,):
             return "mma", 0  # also: without operand blocks only zero blocks are written
-        if _kernel_choice == "umma":
-            return "umma", 1
-        if _kernel_choice == "panel":
+        resolve_counts(self._count(needed))
+        counted = self._counted[needed[0]]
+        if counted.total == 0:
+            return "mma", 0  # no pair anywhere: only zero blocks are written
+        if _kernel_choice != "auto" or needed[0] == 1:
+            return "umma", needed[0]
+        if counted.total <= PANEL_STEP_RATIO * counted.pairs:
             return "umma", 2
-        if bs in PANEL_AUTO_BLOCK_SIZES:
-            wide = self.step_plan(bs, dtype, 2)
-            if wide.n_steps <= PANEL_STEP_RATIO * self.pair.n_pairs:
-                return "umma", 2
         return "umma", 1
+
+    def prepare(self, bs: int, dtype: torch.dtype, n_a: int, n_b: int) -> None:
+        """Builds the plan a launch with these arguments will use."""
+        kernel, width = self.choose(bs, dtype, n_a, n_b)
+        if kernel == "mma":
+            self.pair
+        else:
+            self.step_plan(bs, dtype, width)
 
     def run(self, a: Tensor, b: Tensor, bs: int, bias: Tensor | None = None) -> Tensor:
         """The product; with ``bias`` (data dtype, one element per output column) every output row
@@ -374,3 +471,14 @@ class Product:
                         "bsp_bias_add")
             return out
         return run_step_plan(self.step_plan(bs, a.dtype, width), a, b, bs, bias, self.lut_out)
+
+
+def prepare_products(requests: list[tuple[Product, int, torch.dtype, int, int]]) -> None:
+    """Builds the plans the launches ``(product, block size, dtype, n_a, n_b)`` will use, with the
+    totals of all of them read from the device in one copy."""
+    pending: list[_Counted] = []
+    for product, bs, dtype, n_a, n_b in requests:
+        pending += product._count(product._needed(bs, dtype, n_a, n_b))
+    resolve_counts(pending)
+    for product, bs, dtype, n_a, n_b in requests:
+        product.prepare(bs, dtype, n_a, n_b)
