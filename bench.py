@@ -24,7 +24,9 @@ product computed with torch from the same compressed operands, and a per-batch c
 result gathered over NCCL (the only use of NCCL): rank 0 recomputes one batch of every other rank's
 shard by itself and compares checksums bit for bit.  At N = 1 the line also carries ``also`` (the
 other workloads at full size, each with its own sampled check), ``triton_reference`` (the reference's
-own Triton op on the same GPU and tensors) and ``cpu_baseline`` (the CPU oracle on a bounded sample).
+own Triton op on the same GPU and tensors), ``cold_call`` (one forward call that builds all LUTs and
+plans first; the reference's is in ``triton_reference``) and ``cpu_baseline`` (the CPU oracle on a
+bounded sample).
 ``--impl reference`` times the CPU oracle (dense masked matmul, all host threads) instead.
 """
 from __future__ import annotations
@@ -466,6 +468,31 @@ def _import_reference():
     return ref
 
 
+def cold_call_ms(call, repeats: int = 5) -> float:
+    """Median wall-clock time (ms, device drained on both sides) of a forward call that has to build all
+    of its metadata (no layout cache) and run the product."""
+    times = []
+    for _ in range(repeats + 1):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        call()
+        torch.cuda.synchronize()
+        times.append((time.perf_counter() - t0) * 1e3)
+    return median(times[1:])
+
+
+def our_cold_call_ms(p) -> float:
+    """``cold_call_ms`` of the public op on buffer set 0 of problem ``p``, the library-owned layout caches
+    switched off so that every call rebuilds LUTs and plans."""
+    import blksprs_b200 as bs
+    x, y, _ = p.sets[0]
+    bs.utils.set_implicit_layout_caches(False)
+    try:
+        return cold_call_ms(lambda: bs.ops.matmul(x, p.lxd, y, p.lyd, p.lod, p.bs))
+    finally:
+        bs.utils.set_implicit_layout_caches(True)
+
+
 def time_triton(ref, name: str, layouts_dev, sets, bsz, wm, steps: int, warmup: int) -> dict:
     """``bs.ops.matmul`` of the reference (forward, and forward + backward unless the workload is
     forward-only) with a warm ``layout_cache``, validation on and off; the autotuner runs in the warm-up."""
@@ -498,6 +525,9 @@ def time_triton(ref, name: str, layouts_dev, sets, bsz, wm, steps: int, warmup: 
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1) / steps
             results[f"{label}/{mode}"] = {"ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12}
+        # a call without layout_cache: the reference rebuilds its LUTs (the autotuner has run above)
+        x0, y0, _ = sets[0]
+        results[f"{label}/cold_fwd_ms"] = cold_call_ms(lambda: ref.ops.matmul(x0, lxd, y0, lyd, lod, bsz))
     ref.utils.enable_validation()
     return results
 
@@ -963,6 +993,9 @@ def run_gpu_arm(args):
 
         triton_on(prob, name)
         ours_ms = {name: (line["kernel_only"]["ms_per_step"], line["ms_per_step"])}   # (kernel only, public op)
+        ours_cold = {name: our_cold_call_ms(prob)}
+        line["cold_call"] = {"ms": ours_cold[name], "what": "one forward call through the public op without any "
+                             "layout cache (LUTs, plans, product; validation on), wall clock, median of 5"}
         del graph
         del prob
         torch.cuda.empty_cache()
@@ -973,6 +1006,8 @@ def run_gpu_arm(args):
                 ours_ms[other] = (rec["ms_per_step"], rec["api_ms_per_step"])
                 if other in ("config1", "config2"):
                     triton_on(p, other)
+                    ours_cold[other] = our_cold_call_ms(p)
+                    rec["cold_call_ms"] = ours_cold[other]
                 del p
             except Exception as exc:
                 also[other] = {"error": repr(exc)[:300]}
@@ -984,10 +1019,13 @@ def run_gpu_arm(args):
                     res["speedup_kernel_only"] = res[key]["ms_per_step"] / ours_ms[label][0]
                 if ours_ms[label][1]:
                     res["speedup_public_op"] = res[key]["ms_per_step"] / ours_ms[label][1]
+                if label in ours_cold and "validation_on/cold_fwd_ms" in res:
+                    res["speedup_cold_call"] = res["validation_on/cold_fwd_ms"] / ours_cold[label]
         if ref is not None:
             triton_rec["what"] = ("reference bs.ops.matmul (Triton, BLKSPRS_AUTOTUNE=DEFAULT, autotune excluded) on the "
                                   "same GPU and tensors, warm layout_cache; speedup = reference validation_off time "
-                                  "/ ours (kernel only, and through the public op with validation on)")
+                                  "/ ours (kernel only, and through the public op with validation on); cold = one "
+                                  "forward call without layout_cache, both with validation on")
         try:
             also["attention_chain"] = attention_chain_record(dev, peaks)
         except Exception as exc:

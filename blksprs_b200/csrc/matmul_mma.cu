@@ -786,7 +786,7 @@ matmul_mma_direct_kernel(const T* __restrict__ a, int64_t n_a, const T* __restri
             return bl + 1 >= cur.nb ? n_pairs : e - q_begin;
         };
         int blk_end = block_end(0);
-        // one position; CHECKED = false promises that t - D and t are inside the stream
+        // one position (t >= D); CHECKED = false promises that t is inside the stream (then t - D is too)
         auto step = [&](const bool CHECKED, int t, uint32_t (&fa)[R][X], uint32_t (&fb)[R][X]) {
             const int s = t - D;
             if (!CHECKED || s < n_pairs) {
@@ -807,9 +807,10 @@ matmul_mma_direct_kernel(const T* __restrict__ a, int64_t n_a, const T* __restri
             // the next chunk's first records are asked for one window before they are needed
             if (w == n_windows - 1) load_next_window();
             const int base = w << 5;
-            if (w > 0 && base + 32 <= n_pairs) {
+            if (base + 32 <= n_pairs) {
+                // window 0 starts behind the positions requested before the chunk began
 #pragma unroll 1
-                for (int tt = 0; tt < 32; tt += D) {
+                for (int tt = (w == 0 ? D : 0); tt < 32; tt += D) {
 #pragma unroll
                     for (int d = 0; d < D; ++d) step(false, base + tt + d, ra[d], rb[d]);
                 }
