@@ -250,8 +250,12 @@ def _matmul_eager(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_ou
         # the sizes of all plans this call (and its backward) will use arrive in one device->host copy
         prepare_products(requests)
 
-    out = _BlockSparseMatmul.apply(x, y, layout_cache["packed_indices_x"], layout_cache["packed_indices_y"],
-                                   plans, sparsity_block_size)
+    if torch.is_grad_enabled() and (x.requires_grad or y.requires_grad):
+        out = _BlockSparseMatmul.apply(x, y, layout_cache["packed_indices_x"], layout_cache["packed_indices_y"],
+                                       plans, sparsity_block_size)
+    else:
+        # nothing to differentiate: the product without the autograd node
+        out = plans.forward.run(x, y, sparsity_block_size)
     return BlksprsTensor.wrap(out)
 
 

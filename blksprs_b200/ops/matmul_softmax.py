@@ -153,8 +153,11 @@ def _matmul_softmax_eager(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_l
         if checked:
             plans.n_x, plans.n_y = x.size(0), y.size(0)
             plans.layouts_validated = True
-    out = _MatmulSoftmax.apply(x, y, layout_cache["packed_indices_x"], layout_cache["packed_indices_y"], plans,
-                               sparsity_block_size, float(scale), out_dtype)
+    if torch.is_grad_enabled() and (x.requires_grad or y.requires_grad):
+        out = _MatmulSoftmax.apply(x, y, layout_cache["packed_indices_x"], layout_cache["packed_indices_y"], plans,
+                                   sparsity_block_size, float(scale), out_dtype)
+    else:
+        out = _forward(x, y, plans, sparsity_block_size, float(scale), out_dtype)
     return BlksprsTensor.wrap(out)
 
 
