@@ -1,7 +1,7 @@
 """Benchmark of the block-sparse matmul path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--config config5] [--impl ours|reference|triton]
-    python bench.py --probe softmax|conversion|matmul|attention|nocache [--small]       (side probes, see bench_probes.py)
+    python bench.py --probe softmax|conversion|matmul|attention|regular_attention|nocache [--small]       (side probes, see bench_probes.py)
 
 Default workload = the multi-GPU sweep: bf16, block 128, X (256, 4096, 4096) with a Bernoulli(0.10)
 layout from seed 3, Y (256, 4096, 1024) dense, exact inferred output layout, values N(0, 0.02).  ONE
@@ -1167,7 +1167,7 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the public-op, end-to-end, comparator and CPU legs (for short profiler runs)")
     ap.add_argument("--quick", action="store_true", help="skip the other workloads, the Triton comparator and the CPU leg")
-    ap.add_argument("--probe", choices=["softmax", "conversion", "matmul", "attention", "nocache"], help="run a side probe instead")
+    ap.add_argument("--probe", choices=["softmax", "conversion", "matmul", "attention", "regular_attention", "nocache"], help="run a side probe instead")
     ap.add_argument("--small", action="store_true", help="with --probe: one small case")
     ap.add_argument("--iters", type=int, default=10, help="with --probe: timed iterations")
     args = ap.parse_args()

@@ -2,7 +2,8 @@
 matmul op over every dtype and block size; run through ``bench.py``.
 
 ``python bench.py --probe attention [--small]`` times the attention-score chain (separate ops against the
-fused ``matmul_softmax``).  ``python bench.py --probe softmax|conversion [--small]`` prints one line per case with the achieved
+fused ``matmul_softmax``); ``--probe regular_attention`` the reference's own timing test of attention by parts
+(fp32, block size 32).  ``python bench.py --probe softmax|conversion [--small]`` prints one line per case with the achieved
 bandwidth (algorithmic bytes / CUDA-event time).  ``--small`` runs one case of a few hundred MB, the
 size used for profiler captures.  ``python bench.py --probe matmul`` times the public matmul op
 (forward, forward + backward) for every dtype and block size on a 16 x 2048^3 problem with 25 %
@@ -142,7 +143,84 @@ def nocache(small: bool, iters: int) -> None:
         print(line)
 
 
-PROBES = {"nocache": nocache, "softmax": softmax, "conversion": conversion, "matmul": matmul, "attention": attention}
+def regular_attention(small: bool, iters: int) -> None:
+    """The one timing test the reference ships (test/cases/test_blocksparse.py:1481-1579): attention by
+    parts, ``matmul(Q, K^T) -> * scale -> softmax -> matmul(P, V)``, with 8 heads, head dimension 64,
+    fp32, block size 32, half of the attention blocks kept (no empty row), sequence length 512 / 1024 /
+    2048; three warm-up runs, ten runs timed one by one with CUDA events, the median.  Timed here
+    through this library's ops (the chain, and with ``matmul_softmax`` in place of the first three
+    steps) and, where the reference is importable, through the reference's ops on the same tensors,
+    with both results compared."""
+    import bench
+    ref = None
+    try:
+        ref = bench._import_reference()
+    except Exception as exc:
+        print(f"reference not importable: {exc!r}")
+    heads, d, bsz, kept = 8, 64, 32, 0.5
+    for m in (512,) if small else (512, 1024, 2048):
+        g = torch.Generator().manual_seed(m)
+        rows = m // bsz
+        layout = torch.ones((heads, rows, rows), dtype=torch.bool)
+        for h in range(heads):
+            drop = torch.randperm(rows * rows, generator=g)[:int(rows * rows * (1 - kept))]
+            layout[h, drop // rows, drop % rows] = False
+            for i in torch.nonzero(~layout[h].any(dim=1)).flatten().tolist():
+                layout[h, i, int(torch.randint(0, rows, (1,), generator=g))] = True
+        q, k, v = (torch.randn((heads, m, d), generator=g).cuda() for _ in range(3))
+        l_qkv = torch.ones((heads, rows, d // bsz), dtype=torch.bool, device="cuda")
+        l_attn = layout.cuda()
+        scale = d ** -0.5
+
+        def chain_of(lib):
+            qs, ks, vs = (lib.ops.to_sparse(t, l_qkv, bsz) for t in (q, k, v))
+            kt, l_kt = lib.ops.transpose(ks, l_qkv, bsz)
+            l_out = lib.layouting.build_sparsity_layout_matmul(l_attn, l_qkv)
+            caches = ({}, {}, {})
+
+            def run():
+                scores = lib.ops.matmul(qs, l_qkv, kt, l_kt, l_attn, bsz, layout_cache=caches[0]) * scale
+                probs = lib.ops.softmax(scores, l_attn, bsz, layout_cache=caches[1])
+                return lib.ops.matmul(probs, l_attn, vs, l_qkv, l_out, bsz, layout_cache=caches[2])
+            return run, (qs, kt, l_kt, vs, l_out)
+
+        def median_ms(fn):
+            for _ in range(3):
+                out = fn()
+            torch.cuda.synchronize()
+            times = []
+            for _ in range(10):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1))
+            return sorted(times)[5], out
+
+        ours, (qs, kt, l_kt, vs, l_out) = chain_of(bs)
+        fused_caches = ({}, {})
+
+        def fused():
+            probs = bs.ops.matmul_softmax(qs, l_qkv, kt, l_kt, l_attn, bsz, scale=scale, layout_cache=fused_caches[0])
+            return bs.ops.matmul(probs, l_attn, vs, l_qkv, l_out, bsz, layout_cache=fused_caches[1])
+
+        t_ours, out_ours = median_ms(ours)
+        t_fused, out_fused = median_ms(fused)
+        line = (f"regular attention seq={m}: {t_ours * 1e3:.0f} us (chain of four ops), "
+                f"{t_fused * 1e3:.0f} us (matmul_softmax + matmul)")
+        plain = lambda t: t.as_subclass(torch.Tensor).float()
+        err = float((plain(out_fused) - plain(out_ours)).abs().max())
+        if ref is not None:
+            theirs, _ = chain_of(ref)
+            t_ref, out_ref = median_ms(theirs)
+            err_ref = float((plain(out_ours) - plain(out_ref)).abs().max() / plain(out_ref).abs().max())
+            line += f", reference {t_ref * 1e3:.0f} us; max |ours - reference| = {err_ref:.1e} of max |reference|"
+        print(line + f"; max |fused - chain| = {err:.1e}")
+
+
+PROBES = {"nocache": nocache, "softmax": softmax, "conversion": conversion, "matmul": matmul, "attention": attention,
+          "regular_attention": regular_attention}
 
 
 def run(what: str, small: bool, iters: int) -> None:

@@ -15,7 +15,7 @@ from torch import Tensor
 from .. import _cabi
 from ..utils.blksprs_tensor import BlksprsTensor
 from ..utils.tools import build_layout_indices, build_packed_indices, count_active_blocks, \
-    finalize_layout_cache, prepare_layout_cache
+    finalize_layout_cache, plain_dispatch, prepare_layout_cache
 from ..utils.validation import ensure_contiguous, validate_contiguous, validate_device, validate_dimensions, \
     validate_dtype_supported, validate_sparsity, validate_sparsity_block_size, validate_sparsity_dense
 
@@ -79,6 +79,7 @@ class _ToSparse(torch.autograd.Function):
 
     @staticmethod
     @torch.autograd.function.once_differentiable
+    @plain_dispatch
     def backward(ctx, grad_output: Tensor):
         # the scatter itself: the gradient's shape is the output's, so the op's input checks (and the
         # device reads they need) have nothing to find
@@ -96,6 +97,7 @@ class _ToDense(torch.autograd.Function):
 
     @staticmethod
     @torch.autograd.function.once_differentiable
+    @plain_dispatch
     def backward(ctx, grad_output: Tensor):
         # the gather itself; the number of blocks is the forward input's, no device read needed
         layout = ctx.sparsity_layout
@@ -109,6 +111,7 @@ def _single_full_block(sparsity_layout: Tensor) -> bool:
 
 
 @torch.compiler.disable
+@plain_dispatch
 def _to_sparse_eager(x, sparsity_layout, sparsity_block_size, layout_cache):
     x = ensure_contiguous(x)
     validate_dimensions(x)
@@ -125,6 +128,7 @@ def _to_sparse_eager(x, sparsity_layout, sparsity_block_size, layout_cache):
 
 
 @torch.compiler.disable
+@plain_dispatch
 def _to_dense_eager(x, sparsity_layout, sparsity_block_size, fill_value, layout_cache):
     x = ensure_contiguous(x)
     validate_dimensions(x)

@@ -17,7 +17,7 @@ from .. import _cabi
 from ..plan import Product, prepare_products
 from ..utils.blksprs_tensor import BlksprsTensor
 from ..utils.tools import build_layout_indices, build_packed_indices, cast_for_autocast, count_active_blocks, \
-    finalize_layout_cache, implicit_layout_cache, layout_cache_is_current, prepare_layout_cache
+    finalize_layout_cache, implicit_layout_cache, layout_cache_is_current, plain_dispatch, prepare_layout_cache
 from ..utils.validation import ensure_contiguous, validate_contiguous, validate_device, validate_dimensions, \
     validate_dtype_float, validate_shape, validate_sparsity, validate_sparsity_block_size, \
     validate_sparsity_layout, validation_enabled
@@ -104,6 +104,7 @@ class _BlockSparseMatmul(torch.autograd.Function):
 
     @staticmethod
     @torch.autograd.function.once_differentiable
+    @plain_dispatch
     def backward(ctx, grad_output: Tensor):
         x, y, packed_x, packed_y = ctx.saved_tensors
         plans: _MatmulPlans = ctx.plans
@@ -210,6 +211,7 @@ def _validate_cold(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_o
     validate_sparsity_block_size(sparsity_block_size, x, y)
 
 
+@plain_dispatch
 def _matmul_eager(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_output, sparsity_block_size,
                   layout_cache):
     x, y = ensure_contiguous(x, y)

@@ -23,7 +23,7 @@ from torch import Tensor
 from .. import _cabi
 from ..plan import status_word
 from ..utils.blksprs_tensor import BlksprsTensor
-from ..utils.tools import cast_for_autocast, implicit_layout_cache, layout_cache_is_current
+from ..utils.tools import cast_for_autocast, implicit_layout_cache, layout_cache_is_current, plain_dispatch
 from ..utils.validation import ensure_contiguous, validation_enabled
 from .matmul import _PLANS, _MatmulPlans, _backward_plans, _validate_cold, _validate_warm, \
     matmul_build_layout_cache
@@ -103,6 +103,7 @@ class _MatmulSoftmax(torch.autograd.Function):
 
     @staticmethod
     @torch.autograd.function.once_differentiable
+    @plain_dispatch
     def backward(ctx, grad_output: Tensor):
         x, y, packed_x, packed_y, out = ctx.saved_tensors
         plans: _MatmulPlans = ctx.plans
@@ -126,6 +127,7 @@ class _MatmulSoftmax(torch.autograd.Function):
 
 
 @torch.compiler.disable
+@plain_dispatch
 def _matmul_softmax_eager(x, sparsity_layout_x, y, sparsity_layout_y, sparsity_layout_output, sparsity_block_size,
                           scale, out_dtype, layout_cache):
     x, y = ensure_contiguous(x, y)

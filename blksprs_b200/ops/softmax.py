@@ -12,7 +12,7 @@ from torch import Tensor
 
 from .. import _cabi
 from ..utils.blksprs_tensor import BlksprsTensor
-from ..utils.tools import build_packed_indices, finalize_layout_cache, prepare_layout_cache
+from ..utils.tools import build_packed_indices, finalize_layout_cache, plain_dispatch, prepare_layout_cache
 from ..utils.validation import ensure_contiguous, validate_contiguous, validate_device, validate_dimensions, \
     validate_dtype_float_32, validate_sparsity, validate_sparsity_block_size
 
@@ -40,6 +40,7 @@ class _BlockSparseSoftmax(torch.autograd.Function):
 
     @staticmethod
     @torch.autograd.function.once_differentiable
+    @plain_dispatch
     def backward(ctx, grad_output: Tensor):
         out, packed = ctx.saved_tensors
         B, R, C = ctx.layout_shape
@@ -54,6 +55,7 @@ class _BlockSparseSoftmax(torch.autograd.Function):
 
 
 @torch.compiler.disable
+@plain_dispatch
 def _softmax_eager(x, sparsity_layout, sparsity_block_size, layout_cache):
     x = ensure_contiguous(x)
     validate_dimensions(x)

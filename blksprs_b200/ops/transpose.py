@@ -13,7 +13,7 @@ from torch import Tensor
 from .. import _cabi
 from ..utils.blksprs_tensor import BlksprsTensor
 from ..utils.tools import as_base_tensor, build_layout_indices, build_packed_indices, count_active_blocks, \
-    finalize_layout_cache, prepare_layout_cache
+    finalize_layout_cache, plain_dispatch, prepare_layout_cache
 from ..utils.validation import ensure_contiguous, validate_contiguous, validate_device, validate_dimensions, \
     validate_dtype_supported, validate_sparsity, validate_sparsity_block_size
 
@@ -68,12 +68,14 @@ class _BlockSparseTranspose(torch.autograd.Function):
 
     @staticmethod
     @torch.autograd.function.once_differentiable
+    @plain_dispatch
     def backward(ctx, grad_output: Tensor):
         grad, _ = transpose(grad_output.contiguous(), ctx.layout_t, ctx.sparsity_block_size)
         return Tensor(grad), None, None, None, None
 
 
 @torch.compiler.disable
+@plain_dispatch
 def _transpose_eager(x, sparsity_layout, sparsity_block_size, layout_cache):
     x = ensure_contiguous(x)
 

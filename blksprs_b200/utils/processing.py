@@ -25,7 +25,7 @@ from .. import _cabi
 from ..plan import Product
 from .blksprs_tensor import BlksprsTensor
 from .tools import build_layout_indices, build_packed_indices, cast_for_autocast, count_active_blocks, \
-    finalize_layout_cache, prepare_layout_cache
+    finalize_layout_cache, plain_dispatch, prepare_layout_cache
 from .validation import ensure_contiguous, validate_contiguous, validate_device, validate_dimensions, \
     validate_dtype_float, validate_sparsity, validate_sparsity_block_size, validation_enabled
 
@@ -127,6 +127,7 @@ class _SparseLinear(torch.autograd.Function):
 
     @staticmethod
     @torch.autograd.function.once_differentiable
+    @plain_dispatch
     def backward(ctx, grad_output: Tensor):
         x, w_t = ctx.saved_tensors
         plans: _LinearPlans = ctx.plans
@@ -178,6 +179,7 @@ def _run(x: Tensor, sparsity_layout: Tensor, bs: int, w_t_bs: Tensor, b: Tensor 
 
 
 @torch.compiler.disable
+@plain_dispatch
 def _apply_eager(x, sparsity_layout, sparsity_block_size, linear, bias, layout_cache, cached: bool):
     w = linear.weight
     b = bias if bias is not None else linear.bias

@@ -8,6 +8,7 @@ The cache protocol follows blksprs/utils/tools.py:60-156.
 """
 from __future__ import annotations
 
+import functools
 import threading
 from collections import OrderedDict
 from typing import Any
@@ -23,6 +24,18 @@ LayoutCache = dict[str, Any]
 
 _KEY, _REFS, _STATE = "_blksprs_cache_key", "_blksprs_cache_refs", "_blksprs_cache_state"
 _BOOKKEEPING = frozenset((_KEY, _REFS, _STATE))
+
+
+def plain_dispatch(fn):
+    """Runs ``fn`` with the Python-level ``__torch_function__`` dispatch of tensor subclasses switched
+    off.  Compressed tensors arrive as ``BlksprsTensor`` (a subclass that changes nothing but ``repr``);
+    with the dispatch on, every ``size()``, ``data_ptr()`` or ``is_contiguous()`` an op asks of them
+    costs a few microseconds of handler code, several times the op's own host work."""
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        with torch._C.DisableTorchFunctionSubclass():
+            return fn(*args, **kwargs)
+    return wrapper
 
 
 def as_base_tensor(value: Tensor) -> Tensor:

@@ -11,6 +11,7 @@ import threading
 
 import torch
 from torch import Tensor
+from torch.utils.weak import WeakIdKeyDictionary
 
 _state = threading.local()
 
@@ -112,21 +113,60 @@ def validate_shape(tensor: Tensor, expected_shape, name: str = "Tensor") -> None
         raise ValueError(f"{name} shape {tuple(tensor.shape)} doesn't match expected {expected}")
 
 
+# What the device reads below establish about a layout is remembered per layout object (weakly) together
+# with the state it was established in: version counter, shape, strides, dtype, device.  A later check
+# of the same, unchanged layout then needs no device read; an in-place change bumps the version and the
+# facts are read again.  Inference tensors have no version counter and are never remembered.  (The
+# reference reads on every call: blksprs/utils/validation.py:297-315, 358-366.)
+_layout_facts = WeakIdKeyDictionary()
+
+
+def _layout_state(layout: Tensor) -> tuple:
+    return layout._version, layout.shape, layout.stride(), layout.dtype, layout.device
+
+
+def _known_layout_facts(layout: Tensor) -> dict:
+    """The facts on record for ``layout`` in its current state (a fresh record if there are none)."""
+    if torch.is_inference(layout):
+        return {}
+    state = _layout_state(layout)
+    entry = _layout_facts.get(layout)
+    if entry is None or entry[0] != state:
+        entry = (state, {})
+        _layout_facts[layout] = entry
+    return entry[1]
+
+
 def validate_layout_values(sparsity_layout: Tensor) -> None:
     """Real dtype and only 0/1 entries (bool layouts need no device read)."""
     if sparsity_layout.is_complex():
         raise ValueError("Sparsity layout must not have a complex dtype")
     if sparsity_layout.dtype == torch.bool:
         return
+    facts = _known_layout_facts(sparsity_layout)
+    if facts.get("binary"):
+        return
     if not bool(torch.all((sparsity_layout == 0) | (sparsity_layout == 1))):
         raise ValueError("Sparsity layout values must be either 0 or 1")
+    facts["binary"] = True
+
+
+def active_block_count(sparsity_layout: Tensor) -> int:
+    """Number of non-zero layout entries: one device->host read per layout state."""
+    facts = _known_layout_facts(sparsity_layout)
+    n_active = facts.get("n_active")
+    if n_active is None:
+        n_active = int(torch.sum(sparsity_layout.reshape(-1).to(torch.int)))
+        facts["n_active"] = n_active
+    return n_active
 
 
 def validate_sparsity(sparsity_block_size: int, *pairs: tuple[Tensor, Tensor], counts=None) -> None:
     """Checks compressed tensors against their layouts.
 
     ``counts`` may give the already known number of active blocks per layout
-    (from a warm layout cache); otherwise the count is read from the device.
+    (from a warm layout cache); otherwise the count is read from the device,
+    once per layout state.
     """
     if not validation_enabled():
         return
@@ -141,7 +181,7 @@ def validate_sparsity(sparsity_block_size: int, *pairs: tuple[Tensor, Tensor], c
         if not (tensor.size(-1) == tensor.size(-2) == sparsity_block_size):
             raise ValueError("Blocks not conforming to sparsity block size")
         known = None if counts is None else counts[i]
-        n_active = int(torch.sum(layout.reshape(-1).to(torch.int))) if known is None else known
+        n_active = active_block_count(layout) if known is None else known
         if tensor.size(0) != n_active:
             raise ValueError("Mismatch between sparsity layout and blocks")
 
