@@ -118,6 +118,12 @@ def ptr(t: torch.Tensor | None) -> int | None:
     return t.data_ptr()
 
 
+def aligned(tensor: torch.Tensor) -> torch.Tensor:
+    """``tensor`` itself if its data start on a 16-byte boundary (the kernels move 16-byte vectors), else a
+    copy that does: a contiguous view into the middle of a larger buffer may start anywhere."""
+    return tensor if tensor.data_ptr() % 16 == 0 else tensor.clone(memory_format=torch.contiguous_format)
+
+
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 

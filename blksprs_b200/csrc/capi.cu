@@ -4,6 +4,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include <cstdint>
 
 namespace bsp {
 
@@ -48,5 +49,8 @@ extern "C" int bsp_matmul_mma(const void* a, int64_t n_a, const void* b, int64_t
     if (n_out == 0) return BSP_OK;  // an empty grid is legal (empty output layout)
     if (!out || !offsets) return BSP_ERR_INVALID_ARG;
     if ((n_a > 0 && !a) || (n_b > 0 && !b)) return BSP_ERR_INVALID_ARG;
+    // the kernels move 16-byte vectors
+    if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15)
+        return BSP_ERR_INVALID_ARG;
     return launch_matmul_mma(a, n_a, b, n_b, out, n_out, offsets, pairs, bs, dtype, op, status_word, stream);
 }

@@ -71,6 +71,7 @@ def _forward(x: Tensor, y: Tensor, plans: _MatmulPlans, bs: int, scale: float, o
             scores = scores * scale
         return _softmax_rows(scores, plans, bs).to(out_dtype)
     sp = product.step_plan(bs, x.dtype, width)
+    x, y = _cabi.aligned(x), _cabi.aligned(y)
     e = torch.empty((n_out, bs, bs), dtype=x.dtype, device=device)
     stats = torch.empty((n_out, bs, 2), dtype=torch.float32, device=device)
     out = torch.empty((n_out, bs, bs), dtype=out_dtype, device=device)
@@ -111,7 +112,7 @@ class _MatmulSoftmax(torch.autograd.Function):
         _backward_plans(plans, packed_x, packed_y, x.size(0), y.size(0))
         B, R, C = plans.layouts[2].shape
         probs = out.to(torch.float32)
-        grad = grad_output.contiguous().to(torch.float32)
+        grad = _cabi.aligned(grad_output.contiguous().to(torch.float32))
         grad_scores = torch.empty_like(probs)
         if probs.size(0):
             with _cabi.device_guard(probs.device):

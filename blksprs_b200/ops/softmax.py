@@ -30,6 +30,7 @@ class _BlockSparseSoftmax(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: Tensor, packed: Tensor, layout_shape, bs: int):
         B, R, C = layout_shape
+        x = _cabi.aligned(x)
         out = torch.empty_like(x)
         with torch.cuda.device(x.device):
             _cabi.check(_cabi.lib().bsp_softmax_fwd(_cabi.ptr(x), x.size(0), _cabi.ptr(packed), B, R, C, bs,
@@ -44,7 +45,7 @@ class _BlockSparseSoftmax(torch.autograd.Function):
     def backward(ctx, grad_output: Tensor):
         out, packed = ctx.saved_tensors
         B, R, C = ctx.layout_shape
-        grad_output = grad_output.contiguous().to(torch.float32)
+        grad_output = _cabi.aligned(grad_output.contiguous().to(torch.float32))
         grad_x = torch.empty_like(out)
         with torch.cuda.device(out.device):
             _cabi.check(_cabi.lib().bsp_softmax_bwd(_cabi.ptr(grad_output), _cabi.ptr(out), out.size(0),

@@ -459,8 +459,9 @@ class Product:
         additionally gets the bias: fused into the tcgen05 kernel's epilogue, a second in-place pass
         (``bsp_bias_add``) behind the mma.sync kernel."""
         kernel, width = self.choose(bs, a.dtype, a.size(0), b.size(0))
-        if bias is not None and bias.data_ptr() % 16:
-            bias = bias.clone()
+        a, b = _cabi.aligned(a), _cabi.aligned(b)
+        if bias is not None:
+            bias = _cabi.aligned(bias)
         if kernel == "mma":
             out = run_pair_plan(self.pair, a, b, bs)
             if bias is not None and out.size(0):

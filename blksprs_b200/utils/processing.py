@@ -93,6 +93,7 @@ class _LinearPlans:
 
 def _bias_gradient(grad_output: Tensor, lut_o: Tensor, bs: int, n_cols: int) -> Tensor:
     grad = torch.zeros(n_cols, dtype=torch.float32, device=grad_output.device)
+    grad_output = _cabi.aligned(grad_output)
     if grad_output.size(0):
         with torch.cuda.device(grad_output.device):
             _cabi.check(_cabi.lib().bsp_bias_grad(

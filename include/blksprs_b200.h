@@ -204,7 +204,8 @@ int bsp_plan_schedule(const int32_t* offsets, int64_t n_out, int32_t block_cost,
  * ops/transpose.py.
  *   a, b       compressed operands (n_a, bs, bs), (n_b, bs, bs) of `dtype`
  *   out        compressed result (n_out, bs, bs) of `dtype`; every block is
- *              written (zeros where a block has no pair); fp32 accumulation
+ *              written (zeros where a block has no pair); fp32 accumulation.
+ *              a, b and out must be 16-byte aligned (BSP_ERR_INVALID_ARG)
  *   offsets    int32 (n_out+1), pairs int32 (total,2)
  *   status_word device int32[1] or null: receives BSP_ERR_DEVICE_* when a
  *              kernel meets an out-of-range index or a wait limit; never

@@ -336,3 +336,43 @@ def test_calls_without_a_cache_reuse_library_owned_metadata():
         assert tools.implicit_layout_cache("matmul", lx, ly, lo) is None
     finally:
         bs.utils.set_implicit_layout_caches(True)
+
+
+@pytest.mark.parametrize("bs,dtype", [(16, torch.bfloat16), (32, torch.float32), (64, torch.bfloat16)])
+def test_operands_that_start_off_a_16_byte_boundary(bs, dtype):
+    """A contiguous view into the middle of a larger buffer may start at any element; the kernels move
+    16-byte vectors.  The op gives the same bits as with aligned operands (it copies such an operand
+    first), and the C entry point refuses a misaligned pointer instead of launching."""
+    import blksprs_b200 as bsp
+    from blksprs_b200 import _cabi, plan
+    from blksprs_b200.ops.matmul import matmul_build_layout_cache, _PLANS
+    case = make_case(2, 4 * bs, 4 * bs, 4 * bs, bs, 0.6, dtype, seed=17)
+    lx, ly, lo = (case[k].to(DEV) for k in ("lx", "ly", "lo"))
+    x, y = case["x"].to(DEV), case["y"].to(DEV)
+
+    def shifted(t):
+        base = torch.zeros(t.numel() + 8, dtype=t.dtype, device=t.device)
+        view = base[1:1 + t.numel()].view(t.shape)
+        view.copy_(t)
+        assert view.is_contiguous() and view.data_ptr() % 16 != 0
+        return view
+
+    want = bsp.ops.matmul(x, lx, y, ly, lo, bs)
+    got = bsp.ops.matmul(shifted(x), lx, shifted(y), ly, lo, bs)
+    assert torch.equal(got, want)
+    xs, ys = shifted(x).requires_grad_(True), shifted(y).requires_grad_(True)
+    g = shifted(case["grad"].to(DEV))
+    bsp.ops.matmul(xs, lx, ys, ly, lo, bs).backward(g)
+    xa, ya = x.clone().requires_grad_(True), y.clone().requires_grad_(True)
+    bsp.ops.matmul(xa, lx, ya, ly, lo, bs).backward(case["grad"].to(DEV))
+    assert torch.equal(xs.grad, xa.grad) and torch.equal(ys.grad, ya.grad)
+    # the C entry point itself: no launch, an error code
+    product = matmul_build_layout_cache(None, lx, ly, lo)[_PLANS].forward
+    p = product.pair
+    out = torch.empty((p.n_out, bs, bs), dtype=dtype, device=DEV)
+    status = _cabi.lib().bsp_matmul_mma(
+        shifted(x).data_ptr(), x.size(0), y.data_ptr(), y.size(0), out.data_ptr(), p.n_out, p.offsets.data_ptr(),
+        p.pairs.data_ptr(), bs, _cabi.DATA_DTYPE_CODES[dtype], p.op, plan.status_word(x.device).data_ptr(),
+        _cabi.stream_handle(x.device))
+    assert status == _cabi.ERR_INVALID_ARG
+    torch.cuda.synchronize()
