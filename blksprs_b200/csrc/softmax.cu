@@ -141,9 +141,38 @@ __device__ inline int64_t piece_offset(const int32_t* list, int idx, int vpr_log
     return ((int64_t)blk * bs + row) * bs + piece * 4;
 }
 
+// Four consecutive elements as fp32 (16 bytes of fp32, 8 bytes of a 16-bit type) and back.
+template <typename T> __device__ inline float4 load4(const T* p);
+template <> __device__ inline float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ inline float4 load4<__half>(const __half* p) {
+    const uint2 w = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+template <> __device__ inline float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+    const uint2 w = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename T> __device__ inline void store4(T* p, float4 v);
+template <> __device__ inline void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ inline void store4<__half>(__half* p, float4 v) {
+    const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+template <> __device__ inline void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
+// softmax(scale * x) over the listed blocks of every matrix row; input and output types are free
+// (the arithmetic is fp32).  scale = 1 with fp32 in and out is the reference's op.
+template <typename TI, typename TO>
 __global__ void __launch_bounds__(1024)
-softmax_fwd_list_kernel(const float* __restrict__ x, int64_t n_x, const int64_t* __restrict__ packed,
-                        int64_t n_block_rows, int64_t C, int bs, int vpr_log2, float* __restrict__ out) {
+softmax_fwd_list_kernel(const TI* __restrict__ x, int64_t n_x, const int64_t* __restrict__ packed,
+                        int64_t n_block_rows, int64_t C, int bs, int vpr_log2, float scale, TO* __restrict__ out) {
     extern __shared__ int32_t list[];
     __shared__ int n_active;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
@@ -151,31 +180,32 @@ softmax_fwd_list_kernel(const float* __restrict__ x, int64_t n_x, const int64_t*
         __syncthreads();  // the previous block row's readers are done with the list
         build_block_list(packed + br * C, C, n_x, list, &n_active);
         __syncthreads();
-        const int total = n_active << vpr_log2;  // float4 pieces per matrix row
+        const int total = n_active << vpr_log2;  // pieces of four elements per matrix row
         if (total == 0) continue;
         for (int row = warp; row < bs; row += n_warps) {
             float m = -FLT_MAX;
             for (int idx = lane; idx < total; idx += 32) {
-                const float4 v = *reinterpret_cast<const float4*>(x + piece_offset(list, idx, vpr_log2, row, bs));
-                m = fmaxf(fmaxf(m, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+                const float4 v = load4<TI>(x + piece_offset(list, idx, vpr_log2, row, bs));
+                m = fmaxf(fmaxf(m, fmaxf(v.x * scale, v.y * scale)), fmaxf(v.z * scale, v.w * scale));
             }
             m = warp_max(m);
             float s = 0.f;
             for (int idx = lane; idx < total; idx += 32) {
-                const float4 v = *reinterpret_cast<const float4*>(x + piece_offset(list, idx, vpr_log2, row, bs));
-                s += (fast_exp(v.x - m) + fast_exp(v.y - m)) + (fast_exp(v.z - m) + fast_exp(v.w - m));
+                const float4 v = load4<TI>(x + piece_offset(list, idx, vpr_log2, row, bs));
+                s += (fast_exp(v.x * scale - m) + fast_exp(v.y * scale - m)) +
+                     (fast_exp(v.z * scale - m) + fast_exp(v.w * scale - m));
             }
             s = warp_sum(s);
             const float inv = 1.f / s;
             for (int idx = lane; idx < total; idx += 32) {
                 const int64_t off = piece_offset(list, idx, vpr_log2, row, bs);
-                const float4 v = *reinterpret_cast<const float4*>(x + off);
+                const float4 v = load4<TI>(x + off);
                 float4 o;
-                o.x = fast_exp(v.x - m) * inv;
-                o.y = fast_exp(v.y - m) * inv;
-                o.z = fast_exp(v.z - m) * inv;
-                o.w = fast_exp(v.w - m) * inv;
-                *reinterpret_cast<float4*>(out + off) = o;
+                o.x = fast_exp(v.x * scale - m) * inv;
+                o.y = fast_exp(v.y * scale - m) * inv;
+                o.z = fast_exp(v.z * scale - m) * inv;
+                o.w = fast_exp(v.w * scale - m) * inv;
+                store4<TO>(out + off, o);
             }
         }
     }
@@ -356,8 +386,8 @@ extern "C" int bsp_softmax_fwd(const float* x, int64_t n_x, const int64_t* packe
     if (!x || !packed || !out) return BSP_ERR_INVALID_ARG;
     if (((uintptr_t)x | (uintptr_t)out) & 15) return BSP_ERR_INVALID_ARG;
     if (C <= kListMax && n_x <= INT32_MAX) {
-        softmax_fwd_list_kernel<<<list_grid(B * R, list_warps(bs)), 32 * list_warps(bs), (size_t)C * sizeof(int32_t), (cudaStream_t)stream_>>>(
-            x, n_x, packed, B * R, C, bs, log2_int(bs / 4), out);
+        softmax_fwd_list_kernel<float, float><<<list_grid(B * R, list_warps(bs)), 32 * list_warps(bs), (size_t)C * sizeof(int32_t), (cudaStream_t)stream_>>>(
+            x, n_x, packed, B * R, C, bs, log2_int(bs / 4), 1.0f, out);
     } else {
         softmax_fwd_kernel<<<softmax_grid(n_rows), 256, 0, (cudaStream_t)stream_>>>(x, n_x, packed, n_rows, C, bs, out);
     }
@@ -382,6 +412,43 @@ extern "C" int bsp_softmax_bwd(const float* grad_out, const float* o, int64_t n_
     }
     BSP_LAUNCH_CHECK();
     return BSP_OK;
+}
+
+template <typename TI, typename TO>
+static int launch_softmax_scaled(const void* x, int64_t n_x, const int64_t* packed, int64_t B, int64_t R, int64_t C,
+                                 int bs, float scale, void* out, cudaStream_t stream) {
+    softmax_fwd_list_kernel<TI, TO><<<list_grid(B * R, list_warps(bs)), 32 * list_warps(bs), (size_t)C * sizeof(int32_t), stream>>>(
+        (const TI*)x, n_x, packed, B * R, C, bs, log2_int(bs / 4), scale, (TO*)out);
+    BSP_LAUNCH_CHECK();
+    return BSP_OK;
+}
+template <typename TI>
+static int launch_softmax_scaled_out(int out_dtype, const void* x, int64_t n_x, const int64_t* packed, int64_t B,
+                                     int64_t R, int64_t C, int bs, float scale, void* out, cudaStream_t stream) {
+    switch (out_dtype) {
+        case BSP_F16: return launch_softmax_scaled<TI, __half>(x, n_x, packed, B, R, C, bs, scale, out, stream);
+        case BSP_BF16: return launch_softmax_scaled<TI, __nv_bfloat16>(x, n_x, packed, B, R, C, bs, scale, out, stream);
+        case BSP_F32: return launch_softmax_scaled<TI, float>(x, n_x, packed, B, R, C, bs, scale, out, stream);
+        default: return BSP_ERR_UNSUPPORTED;
+    }
+}
+
+extern "C" int bsp_softmax_fwd_scaled(const void* x, int in_dtype, int64_t n_x, const int64_t* packed, int64_t B,
+                                      int64_t R, int64_t C, int bs, float scale, void* out, int out_dtype,
+                                      void* stream_) {
+    int st = check_softmax_args(n_x, B, R, C, bs);
+    if (st != BSP_OK) return st;
+    if (n_x == 0 || B * R == 0 || C == 0) return BSP_OK;
+    if (!x || !packed || !out) return BSP_ERR_INVALID_ARG;
+    if (((uintptr_t)x | (uintptr_t)out) & 15) return BSP_ERR_INVALID_ARG;
+    if (C > kListMax || n_x > INT32_MAX) return BSP_ERR_UNSUPPORTED;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    switch (in_dtype) {
+        case BSP_F16: return launch_softmax_scaled_out<__half>(out_dtype, x, n_x, packed, B, R, C, bs, scale, out, stream);
+        case BSP_BF16: return launch_softmax_scaled_out<__nv_bfloat16>(out_dtype, x, n_x, packed, B, R, C, bs, scale, out, stream);
+        case BSP_F32: return launch_softmax_scaled_out<float>(out_dtype, x, n_x, packed, B, R, C, bs, scale, out, stream);
+        default: return BSP_ERR_UNSUPPORTED;
+    }
 }
 
 extern "C" int bsp_softmax_normalize(const void* e, int in_dtype, const float* stats, int64_t n_blocks,

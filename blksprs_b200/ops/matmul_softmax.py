@@ -13,7 +13,8 @@ takes the maximum ``m`` of every matrix row inside the block, and writes ``exp(s
 operands' dtype together with ``(m, sum)`` per row and block (8 bytes per ``bs`` elements).  A
 second light pass (``bsp_softmax_normalize``) reads each element once, rescales it with the
 row-wide maximum and sum, and writes the probabilities in ``out_dtype``.  For block sizes 16 and 32
-(no tensor-memory kernel) the op runs matmul, scale and the fp32 softmax kernel one after the other.
+(no tensor-memory kernel) the op runs the mma.sync product and one softmax pass that scales, reads the
+scores in their dtype and writes ``out_dtype`` (``bsp_softmax_fwd_scaled``).
 """
 from __future__ import annotations
 
@@ -23,7 +24,8 @@ from torch import Tensor
 from .. import _cabi
 from ..plan import status_word
 from ..utils.blksprs_tensor import BlksprsTensor
-from ..utils.tools import cast_for_autocast, implicit_layout_cache, layout_cache_is_current, plain_dispatch
+from ..utils.tools import build_packed_indices, cast_for_autocast, implicit_layout_cache, layout_cache_is_current, \
+    plain_dispatch
 from ..utils.validation import ensure_contiguous, validation_enabled
 from .matmul import _PLANS, _MatmulPlans, _backward_plans, _validate_cold, _validate_warm, \
     matmul_build_layout_cache
@@ -46,7 +48,6 @@ def _row_first(plans: _MatmulPlans) -> Tensor:
 
 def _softmax_rows(scores: Tensor, plans: _MatmulPlans, bs: int) -> Tensor:
     """fp32 row-wise softmax over the active blocks (the stand-alone kernel)."""
-    from ..utils.tools import build_packed_indices
     if plans.packed_o is None:
         plans.packed_o = build_packed_indices(plans.layouts[2])
     B, R, C = plans.layouts[2].shape
@@ -66,10 +67,24 @@ def _forward(x: Tensor, y: Tensor, plans: _MatmulPlans, bs: int, scale: float, o
         return torch.empty((0, bs, bs), dtype=out_dtype, device=device)
     kernel, width = product.choose(bs, x.dtype, x.size(0), y.size(0))
     if kernel != "umma":
-        scores = product.run(x, y, bs).float()
-        if scale != 1.0:
-            scores = scores * scale
-        return _softmax_rows(scores, plans, bs).to(out_dtype)
+        # mma.sync product, then scale, softmax and cast in one pass over the scores
+        scores = product.run(x, y, bs)
+        if plans.packed_o is None:
+            plans.packed_o = build_packed_indices(plans.layouts[2])
+        B, R, C = plans.layouts[2].shape
+        out = torch.empty((n_out, bs, bs), dtype=out_dtype, device=device)
+        with _cabi.device_guard(device):
+            status = _cabi.lib().bsp_softmax_fwd_scaled(
+                scores.data_ptr(), _cabi.DATA_DTYPE_CODES[scores.dtype], n_out, plans.packed_o.data_ptr(), B, R, C, bs,
+                float(scale), out.data_ptr(), _cabi.DATA_DTYPE_CODES[out_dtype], _cabi.stream_handle(device))
+        if status == _cabi.ERR_UNSUPPORTED:
+            # very wide layouts: separate steps around the general fp32 softmax kernel
+            scores = scores.float()
+            if scale != 1.0:
+                scores = scores * scale
+            return _softmax_rows(scores, plans, bs).to(out_dtype)
+        _cabi.check(status, "bsp_softmax_fwd_scaled")
+        return out
     sp = product.step_plan(bs, x.dtype, width)
     x, y = _cabi.aligned(x), _cabi.aligned(y)
     e = torch.empty((n_out, bs, bs), dtype=x.dtype, device=device)

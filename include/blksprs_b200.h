@@ -329,6 +329,17 @@ int bsp_to_dense(const void* x, int64_t n_x, const int64_t* packed,
 int bsp_softmax_fwd(const float* x, int64_t n_x, const int64_t* packed,
                     int64_t B, int64_t R, int64_t C, int bs, float* out, void* stream);
 
+/* softmax(scale * x) over the active blocks of every row, with x of any of the
+ * data types and the result in `out_dtype` (fp32 arithmetic): the scale, the
+ * casts and the softmax of the reference's attention-by-parts chain
+ * (test/cases/test_blocksparse.py:1517-1529: matmul, * scale, softmax,
+ * blksprs/ops/softmax.py:23-144) in one pass, used behind the mma.sync matmul
+ * kernels (block size 16 / 32).  BSP_ERR_UNSUPPORTED for layouts with more
+ * than 8192 block columns. */
+int bsp_softmax_fwd_scaled(const void* x, int in_dtype, int64_t n_x, const int64_t* packed,
+                           int64_t B, int64_t R, int64_t C, int bs, float scale,
+                           void* out, int out_dtype, void* stream);
+
 /* grad_x = o * (grad_out - sum_row(grad_out * o)).  Replaces softmax_backward,
  * blksprs/ops/softmax.py:157-208 and :479-520. */
 int bsp_softmax_bwd(const float* grad_out, const float* o, int64_t n_x, const int64_t* packed,

@@ -34,8 +34,10 @@ def _attention_case(B, S, D, bsz, dtype, seed, width=3):
 
 @pytest.mark.parametrize("out_dtype", [None, torch.bfloat16, torch.float32], ids=["same", "bf16", "fp32"])
 @pytest.mark.parametrize("bsz,dtype", [(64, torch.float16), (64, torch.bfloat16), (128, torch.bfloat16), (64, torch.float32),
-                                        (128, torch.float32), (32, torch.float16), (16, torch.float32)],
-                         ids=["bs64-fp16", "bs64-bf16", "bs128-bf16", "bs64-fp32", "bs128-fp32", "bs32-fp16", "bs16-fp32"])
+                                        (128, torch.float32), (32, torch.float16), (16, torch.float32),
+                                        (16, torch.bfloat16), (32, torch.float32)],
+                         ids=["bs64-fp16", "bs64-bf16", "bs128-bf16", "bs64-fp32", "bs128-fp32", "bs32-fp16", "bs16-fp32",
+                              "bs16-bf16", "bs32-fp32"])
 def test_attention_scores_forward_and_backward(bsz, dtype, out_dtype):
     import blksprs_b200 as bs
     B, S, D = 3, 8 * bsz, 2 * bsz
