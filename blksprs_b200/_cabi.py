@@ -69,6 +69,8 @@ SIGNATURES = {
     "bsp_softmax_fwd": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "bsp_softmax_fwd_scaled": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, ctypes.c_float,
                                        c_void_p, c_int, c_void_p]),
+    "bsp_softmax_bwd_scaled": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                       ctypes.c_float, c_void_p, c_int, c_void_p]),
     "bsp_softmax_bwd": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p,
                                 c_void_p]),
     "bsp_bias_add": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p]),

@@ -211,10 +211,13 @@ softmax_fwd_list_kernel(const TI* __restrict__ x, int64_t n_x, const int64_t* __
     }
 }
 
+// grad_x = scale * o * (g - sum_row(g * o)): the gradient with respect to x of softmax(scale * x), given
+// the probabilities o and their gradient g; the three tensors may have different types (fp32 arithmetic).
+template <typename TG, typename TP, typename TX>
 __global__ void __launch_bounds__(1024)
-softmax_bwd_list_kernel(const float* __restrict__ g, const float* __restrict__ o, int64_t n_x,
+softmax_bwd_list_kernel(const TG* __restrict__ g, const TP* __restrict__ o, int64_t n_x,
                         const int64_t* __restrict__ packed, int64_t n_block_rows, int64_t C, int bs,
-                        int vpr_log2, float* __restrict__ grad_x) {
+                        int vpr_log2, float scale, TX* __restrict__ grad_x) {
     extern __shared__ int32_t list[];
     __shared__ int n_active;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
@@ -228,21 +231,21 @@ softmax_bwd_list_kernel(const float* __restrict__ g, const float* __restrict__ o
             float s = 0.f;
             for (int idx = lane; idx < total; idx += 32) {
                 const int64_t off = piece_offset(list, idx, vpr_log2, row, bs);
-                const float4 a = *reinterpret_cast<const float4*>(g + off);
-                const float4 b = *reinterpret_cast<const float4*>(o + off);
+                const float4 a = load4<TG>(g + off);
+                const float4 b = load4<TP>(o + off);
                 s += (a.x * b.x + a.y * b.y) + (a.z * b.z + a.w * b.w);
             }
             s = warp_sum(s);
             for (int idx = lane; idx < total; idx += 32) {
                 const int64_t off = piece_offset(list, idx, vpr_log2, row, bs);
-                const float4 a = *reinterpret_cast<const float4*>(g + off);
-                const float4 b = *reinterpret_cast<const float4*>(o + off);
+                const float4 a = load4<TG>(g + off);
+                const float4 b = load4<TP>(o + off);
                 float4 r;
-                r.x = b.x * (a.x - s);
-                r.y = b.y * (a.y - s);
-                r.z = b.z * (a.z - s);
-                r.w = b.w * (a.w - s);
-                *reinterpret_cast<float4*>(grad_x + off) = r;
+                r.x = b.x * (a.x - s) * scale;
+                r.y = b.y * (a.y - s) * scale;
+                r.z = b.z * (a.z - s) * scale;
+                r.w = b.w * (a.w - s) * scale;
+                store4<TX>(grad_x + off, r);
             }
         }
     }
@@ -404,8 +407,8 @@ extern "C" int bsp_softmax_bwd(const float* grad_out, const float* o, int64_t n_
     if (!grad_out || !o || !packed || !grad_x) return BSP_ERR_INVALID_ARG;
     if (((uintptr_t)grad_out | (uintptr_t)o | (uintptr_t)grad_x) & 15) return BSP_ERR_INVALID_ARG;
     if (C <= kListMax && n_x <= INT32_MAX) {
-        softmax_bwd_list_kernel<<<list_grid(B * R, list_warps(bs)), 32 * list_warps(bs), (size_t)C * sizeof(int32_t), (cudaStream_t)stream_>>>(
-            grad_out, o, n_x, packed, B * R, C, bs, log2_int(bs / 4), grad_x);
+        softmax_bwd_list_kernel<float, float, float><<<list_grid(B * R, list_warps(bs)), 32 * list_warps(bs), (size_t)C * sizeof(int32_t), (cudaStream_t)stream_>>>(
+            grad_out, o, n_x, packed, B * R, C, bs, log2_int(bs / 4), 1.0f, grad_x);
     } else {
         softmax_bwd_kernel<<<softmax_grid(n_rows), 256, 0, (cudaStream_t)stream_>>>(grad_out, o, n_x, packed, n_rows,
                                                                                     C, bs, grad_x);
@@ -447,6 +450,55 @@ extern "C" int bsp_softmax_fwd_scaled(const void* x, int in_dtype, int64_t n_x, 
         case BSP_F16: return launch_softmax_scaled_out<__half>(out_dtype, x, n_x, packed, B, R, C, bs, scale, out, stream);
         case BSP_BF16: return launch_softmax_scaled_out<__nv_bfloat16>(out_dtype, x, n_x, packed, B, R, C, bs, scale, out, stream);
         case BSP_F32: return launch_softmax_scaled_out<float>(out_dtype, x, n_x, packed, B, R, C, bs, scale, out, stream);
+        default: return BSP_ERR_UNSUPPORTED;
+    }
+}
+
+template <typename TG, typename TP, typename TX>
+static int launch_softmax_bwd_scaled(const void* g, const void* o, int64_t n_x, const int64_t* packed, int64_t B,
+                                     int64_t R, int64_t C, int bs, float scale, void* grad_x, cudaStream_t stream) {
+    softmax_bwd_list_kernel<TG, TP, TX><<<list_grid(B * R, list_warps(bs)), 32 * list_warps(bs), (size_t)C * sizeof(int32_t), stream>>>(
+        (const TG*)g, (const TP*)o, n_x, packed, B * R, C, bs, log2_int(bs / 4), scale, (TX*)grad_x);
+    BSP_LAUNCH_CHECK();
+    return BSP_OK;
+}
+template <typename TG, typename TP>
+static int launch_softmax_bwd_scaled_x(int x_dtype, const void* g, const void* o, int64_t n_x, const int64_t* packed,
+                                       int64_t B, int64_t R, int64_t C, int bs, float scale, void* grad_x,
+                                       cudaStream_t stream) {
+    switch (x_dtype) {
+        case BSP_F16: return launch_softmax_bwd_scaled<TG, TP, __half>(g, o, n_x, packed, B, R, C, bs, scale, grad_x, stream);
+        case BSP_BF16: return launch_softmax_bwd_scaled<TG, TP, __nv_bfloat16>(g, o, n_x, packed, B, R, C, bs, scale, grad_x, stream);
+        case BSP_F32: return launch_softmax_bwd_scaled<TG, TP, float>(g, o, n_x, packed, B, R, C, bs, scale, grad_x, stream);
+        default: return BSP_ERR_UNSUPPORTED;
+    }
+}
+template <typename TG>
+static int launch_softmax_bwd_scaled_p(int p_dtype, int x_dtype, const void* g, const void* o, int64_t n_x,
+                                       const int64_t* packed, int64_t B, int64_t R, int64_t C, int bs, float scale,
+                                       void* grad_x, cudaStream_t stream) {
+    switch (p_dtype) {
+        case BSP_F16: return launch_softmax_bwd_scaled_x<TG, __half>(x_dtype, g, o, n_x, packed, B, R, C, bs, scale, grad_x, stream);
+        case BSP_BF16: return launch_softmax_bwd_scaled_x<TG, __nv_bfloat16>(x_dtype, g, o, n_x, packed, B, R, C, bs, scale, grad_x, stream);
+        case BSP_F32: return launch_softmax_bwd_scaled_x<TG, float>(x_dtype, g, o, n_x, packed, B, R, C, bs, scale, grad_x, stream);
+        default: return BSP_ERR_UNSUPPORTED;
+    }
+}
+
+extern "C" int bsp_softmax_bwd_scaled(const void* grad_out, int g_dtype, const void* o, int o_dtype, int64_t n_x,
+                                      const int64_t* packed, int64_t B, int64_t R, int64_t C, int bs, float scale,
+                                      void* grad_x, int x_dtype, void* stream_) {
+    int st = check_softmax_args(n_x, B, R, C, bs);
+    if (st != BSP_OK) return st;
+    if (n_x == 0 || B * R == 0 || C == 0) return BSP_OK;
+    if (!grad_out || !o || !packed || !grad_x) return BSP_ERR_INVALID_ARG;
+    if (((uintptr_t)grad_out | (uintptr_t)o | (uintptr_t)grad_x) & 15) return BSP_ERR_INVALID_ARG;
+    if (C > kListMax || n_x > INT32_MAX) return BSP_ERR_UNSUPPORTED;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    switch (g_dtype) {
+        case BSP_F16: return launch_softmax_bwd_scaled_p<__half>(o_dtype, x_dtype, grad_out, o, n_x, packed, B, R, C, bs, scale, grad_x, stream);
+        case BSP_BF16: return launch_softmax_bwd_scaled_p<__nv_bfloat16>(o_dtype, x_dtype, grad_out, o, n_x, packed, B, R, C, bs, scale, grad_x, stream);
+        case BSP_F32: return launch_softmax_bwd_scaled_p<float>(o_dtype, x_dtype, grad_out, o, n_x, packed, B, R, C, bs, scale, grad_x, stream);
         default: return BSP_ERR_UNSUPPORTED;
     }
 }

@@ -126,17 +126,32 @@ class _MatmulSoftmax(torch.autograd.Function):
         bs = ctx.sparsity_block_size
         _backward_plans(plans, packed_x, packed_y, x.size(0), y.size(0))
         B, R, C = plans.layouts[2].shape
-        probs = out.to(torch.float32)
-        grad = _cabi.aligned(grad_output.contiguous().to(torch.float32))
-        grad_scores = torch.empty_like(probs)
-        if probs.size(0):
+        grad = _cabi.aligned(grad_output.contiguous())
+        if grad.dtype not in _OUT_DTYPES:
+            grad = grad.to(torch.float32)
+        n_out = out.size(0)
+        # dS, the scale and the cast to the operands' dtype in one pass over probabilities and their gradient
+        grad_scores = torch.empty((n_out, bs, bs), dtype=x.dtype, device=out.device)
+        status = _cabi.OK
+        if n_out:
+            with _cabi.device_guard(out.device):
+                status = _cabi.lib().bsp_softmax_bwd_scaled(
+                    grad.data_ptr(), _cabi.DATA_DTYPE_CODES[grad.dtype], out.data_ptr(), _cabi.DATA_DTYPE_CODES[out.dtype],
+                    n_out, plans.packed_o.data_ptr(), B, R, C, bs, float(ctx.scale), grad_scores.data_ptr(),
+                    _cabi.DATA_DTYPE_CODES[x.dtype], _cabi.stream_handle(out.device))
+        if status == _cabi.ERR_UNSUPPORTED:
+            # very wide layouts: separate steps around the general fp32 kernel
+            probs, grad = out.to(torch.float32), grad.to(torch.float32)
+            grad_scores = torch.empty_like(probs)
             with _cabi.device_guard(probs.device):
                 _cabi.check(_cabi.lib().bsp_softmax_bwd(_cabi.ptr(grad), _cabi.ptr(probs), probs.size(0),
                                                         _cabi.ptr(plans.packed_o), B, R, C, bs, _cabi.ptr(grad_scores),
                                                         _cabi.stream_handle(probs.device)), "bsp_softmax_bwd")
-        if ctx.scale != 1.0:
-            grad_scores = grad_scores * ctx.scale
-        grad_scores = grad_scores.to(x.dtype)
+            if ctx.scale != 1.0:
+                grad_scores = grad_scores * ctx.scale
+            grad_scores = grad_scores.to(x.dtype)
+        else:
+            _cabi.check(status, "bsp_softmax_bwd_scaled")
         grad_x = plans.grad_x.run(grad_scores, y, bs) if ctx.needs_input_grad[0] else None
         grad_y = plans.grad_y.run(x, grad_scores, bs) if ctx.needs_input_grad[1] else None
         return grad_x, grad_y, None, None, None, None, None, None

@@ -340,6 +340,16 @@ int bsp_softmax_fwd_scaled(const void* x, int in_dtype, int64_t n_x, const int64
                            int64_t B, int64_t R, int64_t C, int bs, float scale,
                            void* out, int out_dtype, void* stream);
 
+/* Gradient of softmax(scale * x) with respect to x from the probabilities `o`
+ * and their gradient `grad_out`: grad_x = scale * o * (grad_out - sum over the
+ * row of grad_out * o), each tensor in its own data type (fp32 arithmetic): the
+ * casts, blksprs/ops/softmax.py:157-208 and the scale of the backward of the
+ * attention-by-parts chain in one pass.  BSP_ERR_UNSUPPORTED for layouts with
+ * more than 8192 block columns. */
+int bsp_softmax_bwd_scaled(const void* grad_out, int g_dtype, const void* o, int o_dtype, int64_t n_x,
+                           const int64_t* packed, int64_t B, int64_t R, int64_t C, int bs,
+                           float scale, void* grad_x, int x_dtype, void* stream);
+
 /* grad_x = o * (grad_out - sum_row(grad_out * o)).  Replaces softmax_backward,
  * blksprs/ops/softmax.py:157-208 and :479-520. */
 int bsp_softmax_bwd(const float* grad_out, const float* o, int64_t n_x, const int64_t* packed,
