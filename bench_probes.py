@@ -148,8 +148,8 @@ def regular_attention(small: bool, iters: int) -> None:
     parts, ``matmul(Q, K^T) -> * scale -> softmax -> matmul(P, V)``, with 8 heads, head dimension 64,
     fp32, block size 32, half of the attention blocks kept (no empty row), sequence length 512 / 1024 /
     2048; three warm-up runs, ten runs timed one by one with CUDA events, the median.  Timed here
-    through this library's ops (the chain, and with ``matmul_softmax`` in place of the first three
-    steps) and, where the reference is importable, through the reference's ops on the same tensors,
+    through this library's ops (the chain, with ``matmul_softmax`` in place of the first three steps,
+    and that pair replayed from a CUDA graph) and, where the reference is importable, through the reference's ops on the same tensors,
     with both results compared."""
     import bench
     ref = None
@@ -207,8 +207,17 @@ def regular_attention(small: bool, iters: int) -> None:
 
         t_ours, out_ours = median_ms(ours)
         t_fused, out_fused = median_ms(fused)
+        # the fused pair recorded into a CUDA graph: what is left when the host path is taken out
+        side, graph = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            fused()
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+                fused()
+        t_graph, _ = median_ms(lambda: graph.replay())
         line = (f"regular attention seq={m}: {t_ours * 1e3:.0f} us (chain of four ops), "
-                f"{t_fused * 1e3:.0f} us (matmul_softmax + matmul)")
+                f"{t_fused * 1e3:.0f} us (matmul_softmax + matmul), {t_graph * 1e3:.0f} us (the latter replayed from a "
+                f"CUDA graph)")
         plain = lambda t: t.as_subclass(torch.Tensor).float()
         err = float((plain(out_fused) - plain(out_ours)).abs().max())
         if ref is not None:
