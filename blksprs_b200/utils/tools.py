@@ -17,6 +17,7 @@ import torch
 from torch import Tensor, Size
 
 from .. import _cabi
+from .validation import _known_layout_facts
 
 INT32_INDEX_MAX = 2_147_483_647
 
@@ -64,7 +65,12 @@ def _layout_dims(sparsity_layout: Tensor) -> tuple[int, int, int]:
 
 
 def count_active_blocks(sparsity_layout: Tensor) -> int:
-    """Number of non-zero layout entries (one device->host read)."""
+    """Number of non-zero layout entries (one device->host read per layout object and state: the count is
+    remembered with the other facts validation keeps about a layout)."""
+    facts = _known_layout_facts(sparsity_layout)
+    known = facts.get("n_nonzero")
+    if known is not None:
+        return known
     layout = _require_cuda_layout(sparsity_layout)
     numel = layout.numel()
     lib = _cabi.lib()
@@ -75,7 +81,8 @@ def count_active_blocks(sparsity_layout: Tensor) -> int:
         _cabi.check(lib.bsp_count_nonzero(_cabi.ptr(layout), _cabi.LAYOUT_DTYPE_CODES[layout.dtype], numel,
                                           _cabi.ptr(count), _cabi.ptr(ws), ws_bytes,
                                           _cabi.stream_handle(layout.device)), "bsp_count_nonzero")
-        return int(count.item())
+        facts["n_nonzero"] = int(count.item())
+        return facts["n_nonzero"]
 
 
 def build_layout_indices(sparsity_layout: Tensor, n_active: int | None = None) -> Tensor:
