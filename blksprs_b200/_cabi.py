@@ -51,7 +51,7 @@ SIGNATURES = {
     "bsp_umma_max_width": (c_int, [c_int, c_int]),
     "bsp_umma_num_ctas": (c_int, [c_int, c_int, c_int]),
     "bsp_panel_count": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
-                                c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+                                c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "bsp_panel_fill": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
                                c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "bsp_matmul_umma": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p,

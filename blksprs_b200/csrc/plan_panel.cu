@@ -28,8 +28,8 @@ panel_walk_kernel(const int64_t* __restrict__ lut_out, const int32_t* __restrict
                   int64_t n_panels, const int64_t* __restrict__ packed_a, int64_t a_sb, int64_t a_sr,
                   int64_t a_st, const int64_t* __restrict__ packed_b, int64_t b_sb, int64_t b_st,
                   int64_t b_sc, int64_t T, int32_t* __restrict__ counts, int32_t* __restrict__ touched_out,
-                  unsigned long long* __restrict__ stats, const int32_t* __restrict__ step_off,
-                  int32_t* __restrict__ steps) {
+                  unsigned long long* __restrict__ stats, int32_t* __restrict__ block_counts,
+                  const int32_t* __restrict__ step_off, int32_t* __restrict__ steps) {
     const int lane = threadIdx.x & 31;
     const unsigned lt_mask = (1u << lane) - 1u;
     const int64_t warps_total = (int64_t)gridDim.x * (blockDim.x >> 5);
@@ -50,6 +50,7 @@ panel_walk_kernel(const int64_t* __restrict__ lut_out, const int32_t* __restrict
         }
         int32_t n = 0;
         int32_t n_hits = 0;    // (A block, B block) pairs the steps stand for
+        int32_t n_col[kPanelMaxG] = {0, 0, 0, 0};  // the same per block of the panel
         unsigned touched = 0;  // columns hit by earlier steps
         const int32_t base = FILL ? step_off[p] : 0;
         const int32_t last = FILL ? step_off[p + 1] - 1 : -1;
@@ -103,7 +104,14 @@ panel_walk_kernel(const int64_t* __restrict__ lut_out, const int32_t* __restrict
                 }
                 touched |= __shfl_sync(0xffffffffu, inc, 31);
                 n += __popc(votes);
-                if (!FILL) n_hits += __popc(mask);
+                if (!FILL) {
+                    n_hits += __popc(mask);
+                    if (block_counts) {
+#pragma unroll
+                        for (int q = 0; q < kPanelMaxG; ++q)
+                            n_col[q] += __popc(__ballot_sync(0xffffffffu, (mask >> q) & 1u));
+                    }
+                }
             }
         }
         if (!FILL) {
@@ -115,6 +123,17 @@ panel_walk_kernel(const int64_t* __restrict__ lut_out, const int32_t* __restrict
                 if (stats) {
                     atomicMax(stats + 0, (unsigned long long)n);
                     atomicAdd(stats + 1, (unsigned long long)n_hits);
+                }
+                if (block_counts) {
+                    int32_t most = 0;
+#pragma unroll
+                    for (int q = 0; q < kPanelMaxG; ++q) {
+                        if (q < g) {
+                            block_counts[first + q] = n_col[q];
+                            most = n_col[q] > most ? n_col[q] : most;
+                        }
+                    }
+                    if (stats) atomicMax(stats + 2, (unsigned long long)most);
                 }
             }
         }
@@ -133,7 +152,8 @@ static inline unsigned panel_grid(int64_t n) {
 extern "C" int bsp_panel_count(const int64_t* lut_out, const int32_t* panel_first, int64_t n_panels,
                                const int64_t* packed_a, int64_t a_sb, int64_t a_sr, int64_t a_st,
                                const int64_t* packed_b, int64_t b_sb, int64_t b_st, int64_t b_sc, int64_t T,
-                               int32_t* counts_out, int32_t* touched_out, int64_t* stats, void* stream_) {
+                               int32_t* counts_out, int32_t* touched_out, int64_t* stats,
+                               int32_t* block_counts_out, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     if (n_panels < 0 || T < 0) return BSP_ERR_INVALID_ARG;
     if (n_panels == 0) return BSP_OK;
@@ -141,7 +161,7 @@ extern "C" int bsp_panel_count(const int64_t* lut_out, const int32_t* panel_firs
         return BSP_ERR_INVALID_ARG;
     panel_walk_kernel<false><<<panel_grid(n_panels), 256, 0, stream>>>(
         lut_out, panel_first, n_panels, packed_a, a_sb, a_sr, a_st, packed_b, b_sb, b_st, b_sc, T,
-        counts_out, touched_out, (unsigned long long*)stats, nullptr, nullptr);
+        counts_out, touched_out, (unsigned long long*)stats, block_counts_out, nullptr, nullptr);
     BSP_LAUNCH_CHECK();
     return BSP_OK;
 }
@@ -156,7 +176,7 @@ extern "C" int bsp_panel_fill(const int64_t* lut_out, const int32_t* panel_first
     if (!lut_out || !panel_first || !step_offsets || !packed_a || !packed_b) return BSP_ERR_INVALID_ARG;
     panel_walk_kernel<true><<<panel_grid(n_panels), 256, 0, stream>>>(
         lut_out, panel_first, n_panels, packed_a, a_sb, a_sr, a_st, packed_b, b_sb, b_st, b_sc, T, nullptr,
-        nullptr, nullptr, step_offsets, steps_out);
+        nullptr, nullptr, nullptr, step_offsets, steps_out);
     BSP_LAUNCH_CHECK();
     return BSP_OK;
 }

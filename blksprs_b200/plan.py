@@ -111,6 +111,8 @@ class _Counted:
     total: int | None = None
     largest: int | None = None
     pairs: int | None = None        # (A block, B block) pairs the plan stands for
+    block_counts: Tensor | None = None   # panels of several blocks: the pairs of every single output block
+    largest_block: int | None = None
 
 
 def count_pairs(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor, R: int, K: int, C: int) -> _Counted:
@@ -158,7 +160,7 @@ def resolve_counts(pending: list[_Counted]) -> None:
     for c in pending:
         c.total = values[at]
         if c.totals.numel() > 1:
-            c.largest, c.pairs = values[at + 1], values[at + 2]
+            c.largest, c.pairs, c.largest_block = values[at + 1], values[at + 2], values[at + 3]
         else:
             c.pairs = c.total
         at += c.totals.numel()
@@ -245,17 +247,46 @@ def count_steps(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor, R:
         counts = torch.empty(max(n_panels, 1), dtype=torch.int32, device=device)
         touched = torch.empty(max(n_panels, 1), dtype=torch.int32, device=device)
         offsets = torch.empty(n_panels + 1, dtype=torch.int32, device=device)
-        # total steps (from the scan), largest panel and pair count (from the counting kernel)
-        totals = torch.zeros(3, dtype=torch.int64, device=device)
+        # total steps (from the scan); largest panel, pair count and largest single block (from the counting
+        # kernel, which for panels of several blocks also leaves the pair count of every single block: the
+        # counts of the single-block plan, should that one be chosen)
+        totals = torch.zeros(4, dtype=torch.int64, device=device)
+        block_counts = torch.empty(max(n_out, 1), dtype=torch.int32, device=device) if width > 1 else None
         ws_bytes = lib.bsp_plan_workspace_bytes(n_panels)
         ws = torch.empty(ws_bytes // 8, dtype=torch.int64, device=device)
         walk = (_cabi.ptr(lut_out), _cabi.ptr(panel_first), n_panels, _cabi.ptr(packed_a), a_sb, a_sr, a_st,
                 _cabi.ptr(packed_b), b_sb, b_st, b_sc, T)
-        _cabi.check(lib.bsp_panel_count(*walk, _cabi.ptr(counts), _cabi.ptr(touched), totals.data_ptr() + 8, stream),
-                    "bsp_panel_count")
+        _cabi.check(lib.bsp_panel_count(*walk, _cabi.ptr(counts), _cabi.ptr(touched), totals.data_ptr() + 8,
+                                        _cabi.ptr(block_counts), stream), "bsp_panel_count")
         _cabi.check(lib.bsp_plan_offsets(_cabi.ptr(counts), n_panels, _cabi.ptr(offsets), _cabi.ptr(totals),
                                          _cabi.ptr(ws), ws_bytes, stream), "bsp_plan_offsets")
-    return _Counted(width, walk, n_panels, offsets, totals, panel_first, touched)
+    return _Counted(width, walk, n_panels, offsets, totals, panel_first, touched, block_counts=block_counts)
+
+
+def single_block_counts(op: int, lut_out: Tensor, packed_a: Tensor, packed_b: Tensor, R: int, K: int, C: int,
+                        wide: _Counted) -> _Counted:
+    """The counted half of the plan with one block per panel, taken from a resolved count of wider
+    panels: its per-panel counts are the wide walk's per-block pair counts, its totals are known, so
+    neither a second walk nor a second read is needed (only the scan of the counts)."""
+    device = lut_out.device
+    n_out = lut_out.size(0)
+    (a_sb, a_sr, a_st), (b_sb, b_st, b_sc), T = _walk_strides(op, R, K, C)
+    lib = _cabi.lib()
+    with torch.cuda.device(device):
+        stream = _cabi.stream_handle(device)
+        panel_first = torch.arange(0, n_out + 1, dtype=torch.int32, device=device)
+        counts = wide.block_counts
+        touched = (counts > 0).to(torch.int32)
+        offsets = torch.empty(n_out + 1, dtype=torch.int32, device=device)
+        totals = torch.empty(4, dtype=torch.int64, device=device)
+        ws_bytes = lib.bsp_plan_workspace_bytes(n_out)
+        ws = torch.empty(ws_bytes // 8, dtype=torch.int64, device=device)
+        walk = (_cabi.ptr(lut_out), _cabi.ptr(panel_first), n_out, _cabi.ptr(packed_a), a_sb, a_sr, a_st,
+                _cabi.ptr(packed_b), b_sb, b_st, b_sc, T)
+        _cabi.check(lib.bsp_plan_offsets(_cabi.ptr(counts), n_out, _cabi.ptr(offsets), _cabi.ptr(totals),
+                                         _cabi.ptr(ws), ws_bytes, stream), "bsp_plan_offsets")
+    return _Counted(1, walk, n_out, offsets, totals, panel_first, touched, total=wide.pairs,
+                    largest=wide.largest_block, pairs=wide.pairs)
 
 
 def finish_step_plan(op: int, n_out: int, counted: _Counted, n_ctas: int, bs: int) -> StepPlan:
@@ -444,6 +475,10 @@ class Product:
             return "umma", needed[0]
         if counted.total <= PANEL_STEP_RATIO * counted.pairs:
             return "umma", 2
+        if 1 not in self._counted:
+            # the single-block plan's counts come out of the walk just read
+            self._counted[1] = single_block_counts(self.op, self.lut_out, self.packed_a, self.packed_b, *self.dims,
+                                                   counted)
         return "umma", 1
 
     def prepare(self, bs: int, dtype: torch.dtype, n_a: int, n_b: int) -> None:

@@ -235,15 +235,18 @@ int bsp_umma_num_ctas(int dtype, int bs, int width);
  * (int32) = bit mask of the panel columns hit by any step.  panel_first is
  * int32 (n_panels+1): first output block of each panel (any grouping of
  * consecutive output blocks, up to four per panel; blocks of a panel that lie
- * in different layout rows are walked row by row).  stats (int64[2], zeroed by
- * the caller, or null) receives the largest counts_out value and the number
- * of (A block, B block) pairs all steps stand for.  Strides as in
+ * in different layout rows are walked row by row).  stats (int64[3], zeroed by
+ * the caller, or null) receives the largest counts_out value, the number of
+ * (A block, B block) pairs all steps stand for and, with block_counts_out, the
+ * largest entry of that.  block_counts_out (int32 per output block, or null)
+ * receives the pairs of every single output block: the counts of the plan with
+ * one block per panel, which then needs no walk of its own.  Strides as in
  * bsp_plan_count. */
 int bsp_panel_count(const int64_t* lut_out, const int32_t* panel_first, int64_t n_panels,
                     const int64_t* packed_a, int64_t a_sb, int64_t a_sr, int64_t a_st,
                     const int64_t* packed_b, int64_t b_sb, int64_t b_st, int64_t b_sc,
                     int64_t T, int32_t* counts_out, int32_t* touched_out, int64_t* stats,
-                    void* stream);
+                    int32_t* block_counts_out, void* stream);
 
 /* steps_out (int32, (total_steps, 8)): [0] a_block, [1..4] b_block per panel
  * column or -1, [5] control word (bits 0-3 present columns, bits 4-7 columns

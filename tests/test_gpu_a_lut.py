@@ -148,3 +148,40 @@ def test_pair_plan_matches_oracle():
             flat = [p for blk in rebuilt for p in blk]
             assert np.array_equal(np.array(flat).reshape(-1, 2), pairs)
             assert [len(b) for b in rebuilt] == list(np.diff(offs))
+
+
+def test_single_block_plan_taken_from_the_two_block_walk():
+    """The automatic choice walks the LUTs once, for panels of two blocks; when it settles on single-block
+    steps, their counts come out of that walk (per-block pair counts) instead of a second one.  The plan
+    built that way equals the one counted directly, entry for entry, for all three products."""
+    from blksprs_b200 import _cabi, plan
+    from blksprs_b200.ops.matmul import matmul_build_layout_cache, _backward_plans, _PLANS
+    lx = cases.bernoulli_layout((3, 9, 11), 0.35, 61)
+    ly = cases.bernoulli_layout((3, 11, 7), 0.35, 62)
+    lo = cases.bernoulli_layout((3, 9, 7), 0.7, 63)
+    n_x, n_y = int(lx.sum()), int(ly.sum())
+
+    def products():
+        cache = matmul_build_layout_cache(None, lx.to(DEV), ly.to(DEV), lo.to(DEV))
+        plans = cache[_PLANS]
+        _backward_plans(plans, cache["packed_indices_x"], cache["packed_indices_y"], n_x, n_y)
+        return plans.forward, plans.grad_x, plans.grad_y
+
+    old_ratio = plan.PANEL_STEP_RATIO
+    plan.PANEL_STEP_RATIO = 0.0   # two-block panels never pay off: the automatic choice falls to width 1
+    try:
+        derived = []
+        for product in products():
+            assert product.choose(64, torch.bfloat16, 5, 5) == ("umma", 1)
+            assert 2 in product._counted and product._counted[1].block_counts is None
+            derived.append(product.step_plan(64, torch.bfloat16, 1))
+    finally:
+        plan.PANEL_STEP_RATIO = old_ratio
+    for got, product in zip(derived, products()):
+        n_ctas = _cabi.lib().bsp_umma_num_ctas(_cabi.DATA_DTYPE_CODES[torch.bfloat16], 64, 1)
+        want = plan.build_step_plan(product.op, product.lut_out, product.packed_a, product.packed_b, *product.dims,
+                                    1, n_ctas, 64)
+        assert (got.n_panels, got.n_steps, got.n_units) == (want.n_panels, want.n_steps, want.n_units)
+        for name in ("panel_first", "step_offsets", "touched", "unit_panel", "unit_step"):
+            assert torch.equal(getattr(got, name), getattr(want, name)), name
+        assert torch.equal(got.steps[:got.n_steps], want.steps[:want.n_steps])
