@@ -14,7 +14,7 @@ from torch import Tensor
 
 from .. import _cabi
 from ..utils.blksprs_tensor import BlksprsTensor
-from ..utils.tools import build_layout_indices, build_packed_indices, count_active_blocks, \
+from ..utils.tools import build_layout_indices, build_packed_indices, \
     finalize_layout_cache, plain_dispatch, prepare_layout_cache
 from ..utils.validation import ensure_contiguous, validate_contiguous, validate_device, validate_dimensions, \
     validate_dtype_supported, validate_sparsity, validate_sparsity_block_size, validate_sparsity_dense
@@ -34,10 +34,10 @@ def _fill_bits(fill_value, dtype: torch.dtype) -> int:
 
 def to_sparse_build_layout_cache(layout_cache: dict | None, sparsity_layout: Tensor) -> dict:
     layout_cache = prepare_layout_cache(layout_cache, "to_sparse", sparsity_layout)
-    if "n_sparse_blocks" not in layout_cache:
-        layout_cache["n_sparse_blocks"] = count_active_blocks(sparsity_layout)
     if "layout_indices" not in layout_cache:
-        layout_cache["layout_indices"] = build_layout_indices(sparsity_layout, layout_cache["n_sparse_blocks"])
+        layout_cache["layout_indices"] = build_layout_indices(sparsity_layout, layout_cache.get("n_sparse_blocks"))
+    if "n_sparse_blocks" not in layout_cache:
+        layout_cache["n_sparse_blocks"] = layout_cache["layout_indices"].size(0)
     validate_contiguous(sparsity_layout, layout_cache["layout_indices"])
     return finalize_layout_cache(layout_cache)
 

@@ -16,7 +16,7 @@ from torch import Tensor
 from .. import _cabi
 from ..plan import Product, prepare_products
 from ..utils.blksprs_tensor import BlksprsTensor
-from ..utils.tools import build_layout_indices, build_packed_indices, cast_for_autocast, count_active_blocks, \
+from ..utils.tools import build_layout_indices, build_packed_indices, cast_for_autocast, \
     finalize_layout_cache, implicit_layout_cache, layout_cache_is_current, plain_dispatch, prepare_layout_cache
 from ..utils.validation import ensure_contiguous, validate_contiguous, validate_device, validate_dimensions, \
     validate_dtype_float, validate_shape, validate_sparsity, validate_sparsity_block_size, \
@@ -57,11 +57,12 @@ def matmul_build_layout_cache(layout_cache: dict | None, sparsity_layout_x: Tens
         layout_cache["packed_indices_x"] = build_packed_indices(sparsity_layout_x)
     if "packed_indices_y" not in layout_cache:
         layout_cache["packed_indices_y"] = build_packed_indices(sparsity_layout_y)
-    if "n_sparse_blocks" not in layout_cache:
-        layout_cache["n_sparse_blocks"] = count_active_blocks(sparsity_layout_output)
     if "layout_indices_o" not in layout_cache:
+        # counted once: the LUT's row count is the number of active output blocks
         layout_cache["layout_indices_o"] = build_layout_indices(sparsity_layout_output,
-                                                                layout_cache["n_sparse_blocks"])
+                                                                layout_cache.get("n_sparse_blocks"))
+    if "n_sparse_blocks" not in layout_cache:
+        layout_cache["n_sparse_blocks"] = layout_cache["layout_indices_o"].size(0)
     if _PLANS not in layout_cache:
         layout_cache[_PLANS] = _MatmulPlans(sparsity_layout_x, sparsity_layout_y, sparsity_layout_output)
     plans: _MatmulPlans = layout_cache[_PLANS]

@@ -105,7 +105,11 @@ def build_layout_indices(sparsity_layout: Tensor, n_active: int | None = None) -
         _cabi.check(lib.bsp_count_nonzero(_cabi.ptr(layout), code, numel, _cabi.ptr(count), _cabi.ptr(ws),
                                           ws_bytes, stream), "bsp_count_nonzero")
         if n_active is None:
-            n_active = int(count.item())
+            # one count serves the read and the build; the figure is remembered with the layout's other facts
+            facts = _known_layout_facts(sparsity_layout)
+            n_active = facts.get("n_nonzero")
+            if n_active is None:
+                n_active = facts["n_nonzero"] = int(count.item())
         lut = torch.empty((n_active, 3), dtype=torch.int64, device=layout.device)
         _cabi.check(lib.bsp_build_layout_indices(_cabi.ptr(layout), code, B, R, C, _cabi.ptr(lut), n_active,
                                                  _cabi.ptr(ws), ws_bytes, stream), "bsp_build_layout_indices")
