@@ -281,11 +281,14 @@ def sampled_block_check(a, la, b, lb, lo, out, bs, op: str, n_samples: int = 64,
                 ref = torch.matmul(A, Bm).sum(0)
             else:
                 ref = torch.zeros((bs, bs), device=out.device)
-            worst = max(worst, float((out[p].float() - ref).abs().max()))
+            err = float((out[p].float() - ref).abs().max())
+            # a NaN compares false with everything and max() would silently drop it: anything that is not a
+            # finite number counts as an error beyond every tolerance (1e30, which JSON can carry)
+            worst = max(worst, err if math.isfinite(err) else 1e30)
             ref_max = max(ref_max, float(ref.abs().max()))
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev
-    return {"sampled_blocks": int(picks.numel()), "max_rel_err": worst / max(ref_max, 1e-30)}
+    return {"sampled_blocks": int(picks.numel()), "max_rel_err": min(worst / max(ref_max, 1e-30), 1e30)}
 
 
 def batch_checksums(t: torch.Tensor, layout: torch.Tensor) -> torch.Tensor:

@@ -40,6 +40,16 @@ def test_sampled_block_check_accepts_the_oracle_and_sees_a_wrong_block():
     bad = out.clone()
     bad[0] += 1.0   # block 0 is always among the sampled ones
     assert bench.sampled_block_check(x, lx, y, ly, lo, bad, bs_small, "nn", 24)["max_rel_err"] > 1e-2
+    # a result that is not a number must not slip through (NaN compares false with everything)
+    for poison in (float("nan"), float("inf")):
+        bad = out.clone()
+        bad[0, 3, 5] = poison
+        err = bench.sampled_block_check(x, lx, y, ly, lo, bad, bs_small, "nn", 24)["max_rel_err"]
+        assert not (err <= 1e-2), err
+        bad = out.clone()
+        bad[-1] = poison   # the last block is sampled as well; later finite blocks must not reset the verdict
+        err = bench.sampled_block_check(x, lx, y, ly, lo, bad, bs_small, "nn", 24)["max_rel_err"]
+        assert not (err <= 1e-2), err
 
 
 def test_batch_checksums_are_exact_and_per_batch():
