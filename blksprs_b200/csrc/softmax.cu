@@ -168,7 +168,8 @@ template <> __device__ inline void store4<__nv_bfloat16>(__nv_bfloat16* p, float
 }
 
 // softmax(scale * x) over the listed blocks of every matrix row; input and output types are free
-// (the arithmetic is fp32).  scale = 1 with fp32 in and out is the reference's op.
+// (the arithmetic is fp32).  scale = 1 with fp32 in and out is the reference's op.  Two sweeps over a
+// row: maximum and sum together (the sum rescaled as the maximum grows), then the result.
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(1024)
 softmax_fwd_list_kernel(const TI* __restrict__ x, int64_t n_x, const int64_t* __restrict__ packed,
@@ -183,19 +184,22 @@ softmax_fwd_list_kernel(const TI* __restrict__ x, int64_t n_x, const int64_t* __
         const int total = n_active << vpr_log2;  // pieces of four elements per matrix row
         if (total == 0) continue;
         for (int row = warp; row < bs; row += n_warps) {
-            float m = -FLT_MAX;
+            // first sweep: every lane keeps a running maximum and the sum of exp(. - maximum) of its pieces,
+            // rescaling the sum whenever the maximum grows; the lanes' pairs are then merged
+            float m = -FLT_MAX, s = 0.f;
             for (int idx = lane; idx < total; idx += 32) {
                 const float4 v = load4<TI>(x + piece_offset(list, idx, vpr_log2, row, bs));
-                m = fmaxf(fmaxf(m, fmaxf(v.x * scale, v.y * scale)), fmaxf(v.z * scale, v.w * scale));
+                const float a = v.x * scale, b = v.y * scale, c = v.z * scale, d = v.w * scale;
+                const float mp = fmaxf(fmaxf(a, b), fmaxf(c, d));
+                if (mp > m) {
+                    s *= fast_exp(m - mp);   // zero on the first piece: exp of a hugely negative number
+                    m = mp;
+                }
+                s += (fast_exp(a - m) + fast_exp(b - m)) + (fast_exp(c - m) + fast_exp(d - m));
             }
+            const float m_lane = m;
             m = warp_max(m);
-            float s = 0.f;
-            for (int idx = lane; idx < total; idx += 32) {
-                const float4 v = load4<TI>(x + piece_offset(list, idx, vpr_log2, row, bs));
-                s += (fast_exp(v.x * scale - m) + fast_exp(v.y * scale - m)) +
-                     (fast_exp(v.z * scale - m) + fast_exp(v.w * scale - m));
-            }
-            s = warp_sum(s);
+            s = warp_sum(s * fast_exp(m_lane - m));   // lanes without a piece contribute 0 * exp(-huge) = 0
             const float inv = 1.f / s;
             for (int idx = lane; idx < total; idx += 32) {
                 const int64_t off = piece_offset(list, idx, vpr_log2, row, bs);
