@@ -112,3 +112,43 @@ def test_very_wide_block_rows_use_the_plain_kernels():
     grad = torch.randn(out.shape, generator=g)
     out.backward(grad.to(DEV))
     assert torch.allclose(xd.grad.cpu(), oracle.softmax_backward(grad, want, layout, bsz), atol=1e-6, rtol=1e-4)
+
+
+_DT = (torch.float16, torch.bfloat16, torch.float32)
+
+
+@pytest.mark.parametrize("out_dtype", _DT, ids=["to-fp16", "to-bf16", "to-fp32"])
+@pytest.mark.parametrize("in_dtype", _DT, ids=["fp16", "bf16", "fp32"])
+def test_scaled_entry_points_for_every_type_combination(in_dtype, out_dtype):
+    """``bsp_softmax_fwd_scaled`` / ``bsp_softmax_bwd_scaled`` through the C ABI: softmax(scale * x) with x in
+    one data type and the result in another, and its gradient with the gradient in a third, against the
+    fp32 oracle applied to the same (already rounded) inputs."""
+    from blksprs_b200 import _cabi
+    from blksprs_b200.utils.tools import build_packed_indices
+    bsz, B, R, C, scale = 32, 2, 3, 6, 0.37
+    g = torch.Generator().manual_seed(77)
+    layout = random_layout(B, R, C, 0.6, g)
+    n = int(layout.sum())
+    x = (torch.randn((n, bsz, bsz), generator=g) * 3).to(in_dtype)
+    packed = build_packed_indices(layout.to(DEV))
+    xd = x.to(DEV)
+    out = torch.empty((n, bsz, bsz), dtype=out_dtype, device=DEV)
+    lib = _cabi.lib()
+    _cabi.check(lib.bsp_softmax_fwd_scaled(xd.data_ptr(), _cabi.DATA_DTYPE_CODES[in_dtype], n, packed.data_ptr(), B, R, C,
+                                           bsz, scale, out.data_ptr(), _cabi.DATA_DTYPE_CODES[out_dtype],
+                                           _cabi.stream_handle(torch.device(DEV))), "bsp_softmax_fwd_scaled")
+    want = oracle.softmax(x.float() * scale, layout, bsz)
+    tol = 1e-5 if out_dtype == torch.float32 else (1e-3 if out_dtype == torch.float16 else 8e-3)
+    assert float((out.float().cpu() - want).abs().max()) <= tol
+    # gradient: probabilities as stored (out_dtype), their gradient in in_dtype, the result in every type
+    grad = (torch.randn((n, bsz, bsz), generator=g)).to(in_dtype)
+    want_grad = oracle.softmax_backward(grad.float(), out.float().cpu(), layout, bsz) * scale
+    for x_dtype in _DT:
+        gx = torch.empty((n, bsz, bsz), dtype=x_dtype, device=DEV)
+        _cabi.check(lib.bsp_softmax_bwd_scaled(grad.to(DEV).data_ptr(), _cabi.DATA_DTYPE_CODES[in_dtype], out.data_ptr(),
+                                               _cabi.DATA_DTYPE_CODES[out_dtype], n, packed.data_ptr(), B, R, C, bsz, scale,
+                                               gx.data_ptr(), _cabi.DATA_DTYPE_CODES[x_dtype],
+                                               _cabi.stream_handle(torch.device(DEV))), "bsp_softmax_bwd_scaled")
+        ref_max = float(want_grad.abs().max())
+        rel = float((gx.float().cpu() - want_grad).abs().max()) / ref_max
+        assert rel <= (1e-5 if x_dtype == torch.float32 else (2e-3 if x_dtype == torch.float16 else 1e-2)), (x_dtype, rel)
