@@ -118,9 +118,6 @@ def attention(small: bool, iters: int) -> None:
 def nocache(small: bool, iters: int) -> None:
     """Calls WITHOUT a ``layout_cache`` (the reference's default): time per forward call on unchanged layout
     objects, with the library-owned caches on and off, and the reference's op called the same way."""
-    import os
-    import sys
-
     import bench
     ref = None
     try:
